@@ -1,0 +1,301 @@
+#!/usr/bin/env python
+"""Benchmark of the Winograd-ReLU F(2x2,3x3) convolution layer forward (transform + ReLU -> 16 products
+-> output transform) on B200, one process per GPU, batch-sharded (weak scaling, no collective on the path).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--math tf32|fp32]
+                    [--workload cfg2|cfg1|cfg3] [--layout NCHW|NHWC]
+
+Prints ONE JSON line (rank 0).  `value` is images per second through the layer with inputs resident in
+HBM; `e2e` is the same through the public call with host buffers (H2D of X and D2H of Y inside the timed
+region); `roofline` describes the dominant kernel; `cpu_baseline` is the CPU oracle on the host cores.
+`--impl reference` times the reference layer math on the host cores (the reference has no CPU
+implementation of its own -- its CPU kernels exit -- so this is the C restatement under oracle/).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "sparse-winograd-cnn_b200"))
+
+WORKLOADS = {  # per-GPU shapes: B, C, K, H, W, weight density, post-ReLU input
+    "cfg1": dict(B=4, C=64, K=64, H=56, W=56, density=1.0, halfnormal=False),
+    "cfg2": dict(B=64, C=64, K=64, H=56, W=56, density=1.0, halfnormal=False),
+    "cfg3": dict(B=128, C=256, K=256, H=14, W=14, density=0.3, halfnormal=True),
+}
+METRIC = "winograd_relu_conv_layer_fwd_throughput"
+UNIT = "img/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+def make_inputs(wl, seed=1):
+    rng = np.random.default_rng(seed)
+    X = rng.standard_normal((wl["B"], wl["C"], wl["H"], wl["W"]), dtype=np.float32)
+    if wl["halfnormal"]:
+        X = np.maximum(X, 0)
+    rw = np.random.default_rng(2)
+    Wt = (0.05 * rw.standard_normal((16, wl["C"], wl["K"]))).astype(np.float32)
+    if wl["density"] < 1.0:
+        Wt *= (np.random.default_rng(3).random(Wt.shape) < wl["density"]).astype(np.float32)
+    return X, Wt
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._stop = index, [], threading.Event()
+
+    def run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([f.strip() for f in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def finish(self):
+        self._stop.set()
+        self.join(timeout=6)
+        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return dict(sm_mhz=float(np.median(sm)) if sm else None,
+                    sm_max_mhz=float(self.rows[0][1]) if self.rows else None, reasons=reasons, samples=len(self.rows))
+
+
+def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
+    """Images per second of the C oracle (float32, OpenMP over all host cores) on a batch slice."""
+    from oracle import wg_oracle as o
+    b = sample_b or max(1, min(wl["B"], 4))
+    X, Wt = make_inputs(dict(wl, B=b))
+    Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
+    P = b * ((wl["H"] + 1) // 2) * ((wl["W"] + 1) // 2)
+    bufs = (np.empty((b, wl["H"], wl["W"], wl["K"]), np.float32), np.empty(16 * P * wl["C"], np.float32),
+            np.empty(16 * P * wl["K"], np.float32))
+    o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)  # warm
+    n, t0 = 0, time.perf_counter()
+    while True:
+        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > seconds or n >= 200:
+            break
+    cores = len(os.sched_getaffinity(0))
+    return dict(value=b * n / dt, unit=UNIT, cores=cores, kind="port",
+                sample="batch slice of %d images of the %dx%dx%dx%d layer, %d passes in %.1f s, float32 C restatement with OpenMP"
+                       % (b, wl["C"], wl["K"], wl["H"], wl["W"], n, dt)), b, dt / n
+
+
+def run_reference(args, wl, rank, world):
+    if rank != 0:
+        return
+    from oracle import wg_oracle as o
+    b = max(1, min(wl["B"], 4))
+    X, Wt = make_inputs(dict(wl, B=b))
+    Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
+    P = b * ((wl["H"] + 1) // 2) * ((wl["W"] + 1) // 2)
+    bufs = (np.empty((b, wl["H"], wl["W"], wl["K"]), np.float32), np.empty(16 * P * wl["C"], np.float32),
+            np.empty(16 * P * wl["K"], np.float32))
+    for _ in range(args.warmup):
+        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+    dt = time.perf_counter() - t0
+    val = b * args.steps / dt
+    cores = len(os.sched_getaffinity(0))
+    sample = "each step = batch slice of %d images of the workload (host cores, OpenMP, float32)" % b
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "layer": wl, "layout": "NHWC", "sample_batch": b},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships GPU-only ops (its CPU kernels exit); this arm is the C restatement of its layer math",
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--math", default=os.environ.get("WG2X2_BENCH_MATH", "tf32"), choices=["tf32", "fp32"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import wg2x2  # raises if the CUDA library is missing: there is no fallback
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, C, K, H, W = wl["B"], wl["C"], wl["K"], wl["H"], wl["W"]
+    nH, nW = (H + 1) // 2, (W + 1) // 2
+    P = B * nH * nW
+    Xh, Wth = make_inputs(wl, seed=1 + rank)
+    if args.layout == "NHWC":
+        Xh = np.ascontiguousarray(np.transpose(Xh, (0, 2, 3, 1)))
+    NBUF = 4  # rotating inputs: 4 |X| + the V/Y traffic of a step is well beyond the 126 MB L2
+    Xs = [torch.from_numpy(Xh).to(dev) + 0.0 * i for i in range(NBUF)]
+    Wt = torch.from_numpy(Wth).to(dev)
+    V = torch.empty((16, B, nH, nW, C), device=dev)
+    Y = torch.empty((B, K, H, W) if args.layout == "NCHW" else (B, H, W, K), device=dev)
+    ws_n = wg2x2._lib.lib.wg2x2_conv_fwd_workspace_bytes(B, nH, nW, C, K, wg2x2.ops._MATHS[args.math])
+    ws = torch.empty(max(ws_n, 1), dtype=torch.uint8, device=dev)
+
+    def step(i):
+        wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
+        wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    # per-kernel events inside the timed region (for the roofline of the dominant kernel)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(args.steps):
+        ev[i][0].record()
+        wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
+        ev[i][1].record()
+        wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
+        ev[i][2].record()
+    t_end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.finish()
+    ms_total = t_start.elapsed_time(t_end)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    ms_k1 = float(np.mean([e[0].elapsed_time(e[1]) for e in ev]))
+    ms_k2 = float(np.mean([e[1].elapsed_time(e[2]) for e in ev]))
+    status, where = wg2x2.last_device_status()
+    if status != 0:
+        raise RuntimeError("device status %d at %d" % (status, where))
+
+    # ---- end to end through the public call with host buffers ------------------------------
+    Xpin = torch.from_numpy(Xh).pin_memory()
+    Ypin = torch.empty(Y.shape, dtype=torch.float32).pin_memory()
+    Xd = torch.empty_like(Xs[0])
+    lws_n = wg2x2._lib.lib.wg2x2_layer_fwd_workspace_bytes(B, H, W, C, K, wg2x2.ops._MATHS[args.math], 0)
+    lws = torch.empty(max(lws_n, 1), dtype=torch.uint8, device=dev)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        Xd.copy_(Xpin, non_blocking=True)
+        wg2x2.layer_fwd(Xd, Wt, relu=True, layout=args.layout, math=args.math, out=Y, workspace=lws)
+        Ypin.copy_(Y, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    te = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e2e_steps
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    bytesX, bytesV, bytesY, bytesW = 4 * B * C * H * W, 64 * P * C, 4 * B * K * H * W, 64 * C * K
+    flops = 2.0 * 16 * P * C * K
+    k1_bytes, k2_bytes = bytesX + bytesV, bytesV + bytesW + bytesY
+    tf32_peak = pk["bf16_tflops"] / 2.0
+    k2_t_hbm, k2_t_tensor = k2_bytes / (pk["hbm_gbs"] * 1e9), flops / (tf32_peak * 1e12)
+    if ms_k2 >= ms_k1:
+        if args.math == "tf32" and k2_t_tensor > k2_t_hbm:
+            roof = dict(kernel="conv_fwd (products + output transform)", bound="tensor", achieved=flops / (ms_k2 * 1e-3) / 1e12,
+                        peak=tf32_peak, unit="TFLOP/s", peak_source=pk["source"] + " bf16 / 2")
+        else:
+            roof = dict(kernel="conv_fwd (products + output transform)", bound="hbm", achieved=k2_bytes / (ms_k2 * 1e-3) / 1e9,
+                        peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"])
+    else:
+        roof = dict(kernel="imtrans_fwd (input transform + ReLU)", bound="hbm", achieved=k1_bytes / (ms_k1 * 1e-3) / 1e9,
+                    peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"])
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["kernels_ms"] = {"imtrans_fwd": ms_k1, "conv_fwd": ms_k2}
+    roof["imtrans_fwd_gbs"] = k1_bytes / (ms_k1 * 1e-3) / 1e9
+    roof["conv_fwd_gbs"] = k2_bytes / (ms_k2 * 1e-3) / 1e9
+    roof["conv_fwd_tflops"] = flops / (ms_k2 * 1e-3) / 1e12
+
+    out = {
+        "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
+                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((k1_bytes + k2_bytes) / 1e6)},
+        "layer_gbs_two_kernel": (k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
+        "layer_tflops": flops * world / (ms_step * 1e-3) / 1e12,
+        "roofline": roof, "clocks": clocks,
+        "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": bytesX, "d2h_bytes_per_step": bytesY,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": args.steps * 2,
+    }
+    if not args.no_cpu_baseline:
+        cb, _, _ = cpu_oracle_rate(wl, args.layout)
+        out["cpu_baseline"] = cb
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

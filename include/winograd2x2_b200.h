@@ -1,0 +1,117 @@
+/*
+ * winograd2x2_b200 — C ABI of the B200 (sm_100a) Winograd-ReLU F(2x2,3x3) convolution path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the
+ * caller's CUDA stream (a cudaStream_t passed as void*; NULL = the default stream),
+ * allocates nothing, never synchronises the device and never aborts: the return value
+ * is a wg2x2_status.  The caller owns every buffer, scratch included.  Inputs are never
+ * written.
+ *
+ * Tensor layouts
+ *   image-like tensors X, Y, dX, dY : `layout` = WG2X2_NHWC (B,H,W,C) — the reference's —
+ *                                     or WG2X2_NCHW (B,C,H,W)
+ *   V, dV : (16, B, nH, nW, C), nH=(H+1)/2, nW=(W+1)/2, Winograd position t=4*row+col
+ *   W, dW, mask : (16, C, K)
+ * all fp32, dense, contiguous.  Padding is 1 and the tile stride is 2, as the reference
+ * hard-wires them at every call site (e.g. winograd2x2_imTrans_op.cc:55).
+ */
+#ifndef WINOGRAD2X2_B200_H
+#define WINOGRAD2X2_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    WG2X2_OK = 0,
+    WG2X2_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unknown enum, misaligned buffer */
+    WG2X2_ERR_WORKSPACE = -2,   /* workspace missing or smaller than the *_workspace_bytes query */
+    WG2X2_ERR_LAUNCH = -3,      /* the CUDA runtime refused a launch (cudaGetLastError != success) */
+    WG2X2_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up (reported by wg2x2_last_device_status) */
+    WG2X2_ERR_UNSUPPORTED = -5  /* shape outside what the selected math mode supports */
+} wg2x2_status;
+
+enum { WG2X2_NHWC = 0, WG2X2_NCHW = 1 };
+
+/* WG2X2_MATH_FP32: FFMA on the CUDA cores, fp32 accumulate (max rel err <= 1e-5 vs float64).
+ * WG2X2_MATH_TF32: tcgen05 kind::tf32 tensor-core MMAs accumulating in TMEM (<= 5e-3). */
+enum { WG2X2_MATH_FP32 = 0, WG2X2_MATH_TF32 = 1 };
+
+const char *wg2x2_status_string(int status);
+
+/* Version of this ABI (bumped when a signature changes). */
+int wg2x2_abi_version(void);
+
+/*
+ * Input transform V = B^T d B over 4x4 tiles at stride 2, pad 1, optionally followed by
+ * the Winograd-domain ReLU (relu != 0).
+ * Replaces Winograd2x2ImTransComputeLauncher (winograd2x2_imTrans_op.cc:30,
+ * winograd2x2_imTrans_cuda.cu.cc:151-157) and, with relu, the tf.nn.relu the layer wrapper
+ * applies to its result (ResNet-18-var/winograd_imtrans.py:16-17).
+ */
+int wg2x2_imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu,
+                      void *stream);
+
+/*
+ * Gradient of the input transform: dX = overlap-add of B g B^T over the tiles covering each
+ * pixel.  dV is read, never written (the reference transforms it in place).  V_relu, when
+ * not NULL, is the saved forward output of wg2x2_imtrans_fwd(relu=1): the gradient is taken
+ * as zero where V_relu <= 0 (the ReluGrad step).  H, W are the true image sizes.
+ * Replaces Winograd2x2ImTransGradComputeLauncher (winograd2x2_imTrans_grad_op.cc:29,
+ * winograd2x2_imTrans_grad_cuda.cu.cc:118-129).
+ */
+int wg2x2_imtrans_bwd(const float *dV, const float *V_relu, float *dX, int B, int H, int W, int C,
+                      int layout, void *stream);
+
+/*
+ * Winograd-domain product and output transform: Y = A^T (V_t . W_t) A, cropped to
+ * out_h x out_w (2nH-1 <= out_h <= 2nH, same for w).
+ * Replaces Winograd2x2ConvComputeLauncher (winograd2x2_conv_op.cc:31,
+ * winograd2x2_conv_cuda.cu.cc:65-93): the 16 cublasSgemmBatched products and the
+ * Output_transform kernel become one kernel; no product tensor is stored.
+ * workspace: see wg2x2_conv_fwd_workspace_bytes (0 bytes for WG2X2_MATH_FP32).
+ */
+int wg2x2_conv_fwd(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K,
+                   int out_h, int out_w, int layout, int math, void *workspace, size_t workspace_bytes,
+                   void *stream);
+size_t wg2x2_conv_fwd_workspace_bytes(int B, int nH, int nW, int C, int K, int math);
+
+/*
+ * Gradient of the product/output-transform op for dY of size (B,H,W,K):
+ *   dV_t = (A dY A^T)_t . W_t^T   (skipped when dV == NULL)
+ *   dW_t = V_t^T . (A dY A^T)_t   (skipped when dW == NULL), multiplied by mask when mask != NULL
+ * relu != 0 additionally zeroes dV where V <= 0, folding the ReluGrad of the layer wrapper
+ * into this op.  Rows/columns of the tile grid beyond H, W count as zero gradient.
+ * Replaces Winograd2x2ConvGradComputeLauncher (winograd2x2_conv_grad_op.cc:32,
+ * winograd2x2_conv_grad_cuda.cu.cc:79-124) and the mask product autodiff derives from
+ * ResNet-18-var/winograd_conv.py:23-26.
+ */
+int wg2x2_conv_bwd(const float *V, const float *Wt, const float *dY, const float *mask, float *dV,
+                   float *dW, int B, int H, int W, int C, int K, int layout, int relu, int math,
+                   void *workspace, size_t workspace_bytes, void *stream);
+size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int want_dW);
+
+/*
+ * Whole layer forward, X -> Y = conv(relu?(imtrans(X)), W): the call pair at
+ * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119.  V_out, when not NULL, receives
+ * the transformed (post-ReLU) input for a later backward pass; when NULL it lives in the
+ * workspace.
+ */
+int wg2x2_layer_fwd(const float *X, const float *Wt, float *Y, float *V_out, int B, int H, int W, int C,
+                    int K, int layout, int relu, int math, void *workspace, size_t workspace_bytes,
+                    void *stream);
+size_t wg2x2_layer_fwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int keep_V);
+
+/*
+ * Status word of the most recent kernel on this device that uses bounded waits
+ * (the tcgen05 path): 0, or WG2X2_ERR_TIMEOUT with a code saying where it gave up.
+ * Synchronises the given stream.
+ */
+int wg2x2_last_device_status(void *stream, unsigned int *where);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WINOGRAD2X2_B200_H */

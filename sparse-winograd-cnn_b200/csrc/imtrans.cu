@@ -1,0 +1,299 @@
+// Input transform (+ Winograd-domain ReLU) and its gradient.  HBM-bound kernels:
+//   forward  : reads |X| once from HBM (the 4x overlap between neighbouring tiles is served
+//              by L1/L2 or by the shared-memory stage), writes 16 planes of V = 4|X|
+//   backward : reads dV (and V when the ReLU mask is asked for), writes dX; a gather, so it
+//              is deterministic and needs neither atomics nor scratch memory.
+#include "wg_common.cuh"
+
+namespace wg {
+
+template <int VEC> struct Vec;
+template <> struct Vec<4> { using type = float4; };
+template <> struct Vec<1> { using type = float; };
+
+__device__ __forceinline__ float4 ldg(const float4 *p) { return __ldg(p); }
+__device__ __forceinline__ float ldg(const float *p) { return __ldg(p); }
+__device__ __forceinline__ float4 zero_of(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ float zero_of(float) { return 0.f; }
+__device__ __forceinline__ float4 relu_of(float4 a) { return make_float4(fmaxf(a.x, 0.f), fmaxf(a.y, 0.f), fmaxf(a.z, 0.f), fmaxf(a.w, 0.f)); }
+__device__ __forceinline__ float relu_of(float a) { return fmaxf(a, 0.f); }
+__device__ __forceinline__ float4 keep_where_pos(float4 g, float4 m) { return make_float4(m.x > 0.f ? g.x : 0.f, m.y > 0.f ? g.y : 0.f, m.z > 0.f ? g.z : 0.f, m.w > 0.f ? g.w : 0.f); }
+__device__ __forceinline__ float keep_where_pos(float g, float m) { return m > 0.f ? g : 0.f; }
+
+// ------------------------------------------------------------------------------------------
+// Forward, NHWC.  One thread = one tile x VEC channels; consecutive threads walk the channel
+// axis first, so each of the 16 plane stores of a warp is one contiguous run.
+// ------------------------------------------------------------------------------------------
+template <int VEC>
+__global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__restrict__ X, float *__restrict__ V,
+                                                                 int B, int H, int W, int C, int nH, int nW, int relu)
+{
+    using T = typename Vec<VEC>::type;
+    const int CV = C / VEC;
+    const long long total = (long long)B * nH * nW * CV;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = (int)(idx % CV);
+    const long long p = idx / CV;
+    const int tw = (int)(p % nW);
+    const int th = (int)((p / nW) % nH);
+    const int b = (int)(p / ((long long)nW * nH));
+
+    const T *Xv = reinterpret_cast<const T *>(X);
+    T d[4][4];
+#pragma unroll
+    for (int y = 0; y < 4; ++y) {
+        const int fy = 2 * th - 1 + y;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int fx = 2 * tw - 1 + x;
+            const bool in = (fy >= 0) && (fy < H) && (fx >= 0) && (fx < W);
+            d[y][x] = in ? ldg(Xv + (((long long)b * H + fy) * W + fx) * CV + cv) : zero_of(T());
+        }
+    }
+    T v[4][4];
+    bt_d_b(d, v);
+    T *Vv = reinterpret_cast<T *>(V);
+    const long long plane = (long long)B * nH * nW * CV;
+    const long long off = p * CV + cv;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            Vv[(long long)(4 * i + j) * plane + off] = relu ? relu_of(v[i][j]) : v[i][j];
+}
+
+// ------------------------------------------------------------------------------------------
+// Forward, NCHW.  The image axis W is contiguous and tiles overlap along it, so a CTA stages
+// the 4 input rows of one tile row, for CCH channels and TSEG tiles, in shared memory
+// (coalesced along W), then computes with the channel index fastest across a warp so that
+// the plane stores are contiguous along C.
+// ------------------------------------------------------------------------------------------
+constexpr int kCCH = 32;                       // channels per CTA
+constexpr int kTSEG = 32;                      // tiles along W per CTA
+constexpr int kRowPitch = 2 * kTSEG + 2;       // 66 pixels feed 32 tiles
+constexpr int kChanPitch = 4 * kRowPitch + 1;  // odd, so 32 channels hit 32 different banks
+
+__global__ void __launch_bounds__(256) imtrans_fwd_nchw_kernel(const float *__restrict__ X, float *__restrict__ V,
+                                                                 int B, int H, int W, int C, int nH, int nW, int relu)
+{
+    __shared__ float S[kCCH * kChanPitch];
+    const int nseg = cdiv(nW, kTSEG);
+    int bx = blockIdx.x;
+    const int seg = bx % nseg; bx /= nseg;
+    const int th = bx % nH;
+    const int b = bx / nH;
+    const int c0 = blockIdx.y * kCCH;
+    const int tw0 = seg * kTSEG;
+    const int tid = threadIdx.x;
+
+    for (int idx = tid; idx < kCCH * 4 * kRowPitch; idx += 256) {
+        const int x = idx % kRowPitch;
+        const int y = (idx / kRowPitch) & 3;
+        const int c = idx / (4 * kRowPitch);
+        const int gx = 2 * tw0 - 1 + x, gy = 2 * th - 1 + y;
+        float val = 0.f;
+        if (c0 + c < C && gx >= 0 && gx < W && gy >= 0 && gy < H)
+            val = __ldg(X + (((long long)b * C + c0 + c) * H + gy) * W + gx);
+        S[c * kChanPitch + y * kRowPitch + x] = val;
+    }
+    __syncthreads();
+
+    const int c = tid & 31;
+    const long long plane = (long long)B * nH * nW * C;
+#pragma unroll 1
+    for (int it = 0; it < kTSEG / 8; ++it) {
+        const int twl = (tid >> 5) + 8 * it;
+        const int tw = tw0 + twl;
+        if (tw >= nW || c0 + c >= C) continue;
+        float d[4][4], v[4][4];
+#pragma unroll
+        for (int y = 0; y < 4; ++y)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) d[y][x] = S[c * kChanPitch + y * kRowPitch + 2 * twl + x];
+        bt_d_b(d, v);
+        const long long off = (((long long)b * nH + th) * nW + tw) * C + c0 + c;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                V[(long long)(4 * i + j) * plane + off] = relu ? fmaxf(v[i][j], 0.f) : v[i][j];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Backward gather for one 2x2 output block (bh,bw) and VEC channels.
+// dX[2bh+a][2bw+e] = sum over the 3x3 neighbourhood of tiles of G[y][x], y = a+1-2*dth,
+// x = e+1-2*dtw, G = B g B^T, i.e. G[y][x] = sum_ij BT[i][y] BT[j][x] g[i][j].
+// Everything below is unrolled with compile-time coefficients: the centre tile contributes
+// its 16 values, the 4 edge neighbours 4 each, the 4 corner neighbours one each.
+// ------------------------------------------------------------------------------------------
+__host__ __device__ constexpr bool row_needed(int dt, int i)
+{
+    // dt=0 touches y in {1,2} (all i); dt=-1 touches y=3 (i=3 only); dt=+1 touches y=0 (i=0 only)
+    return dt == 0 ? true : (dt < 0 ? i == 3 : i == 0);
+}
+
+template <typename T, bool MASK>
+__device__ __forceinline__ void imtrans_bwd_block(const T *__restrict__ dV, const T *__restrict__ Vm, long long plane,
+                                                  int b, int bh, int bw, int nH, int nW, int CV, int cv, T (&out)[2][2])
+{
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) out[a][e] = zero_of(T());
+#pragma unroll
+    for (int dth = -1; dth <= 1; ++dth) {
+        const int th = bh + dth;
+        if (th < 0 || th >= nH) continue;
+#pragma unroll
+        for (int dtw = -1; dtw <= 1; ++dtw) {
+            const int tw = bw + dtw;
+            if (tw < 0 || tw >= nW) continue;
+            const long long base = (((long long)b * nH + th) * nW + tw) * CV + cv;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (!row_needed(dth, i) || !row_needed(dtw, j)) continue;
+                    T g = ldg(dV + (long long)(4 * i + j) * plane + base);
+                    if (MASK) g = keep_where_pos(g, ldg(Vm + (long long)(4 * i + j) * plane + base));
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int y = a + 1 - 2 * dth, x = e + 1 - 2 * dtw;
+                            if (y < 0 || y > 3 || x < 0 || x > 3) continue;
+                            const int cf = bt_coef(i, y) * bt_coef(j, x);
+                            if (cf > 0) out[a][e] = out[a][e] + g;
+                            if (cf < 0) out[a][e] = out[a][e] - g;
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int VEC, bool MASK>
+__global__ void __launch_bounds__(256) imtrans_bwd_nhwc_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                 float *__restrict__ dX, int B, int H, int W, int C, int nH, int nW)
+{
+    using T = typename Vec<VEC>::type;
+    const int CV = C / VEC;
+    const long long total = (long long)B * nH * nW * CV;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int cv = (int)(idx % CV);
+    const long long p = idx / CV;
+    const int bw = (int)(p % nW);
+    const int bh = (int)((p / nW) % nH);
+    const int b = (int)(p / ((long long)nW * nH));
+    T out[2][2];
+    imtrans_bwd_block<T, MASK>(reinterpret_cast<const T *>(dV), reinterpret_cast<const T *>(Vm),
+                               (long long)B * nH * nW * CV, b, bh, bw, nH, nW, CV, cv, out);
+    T *dXv = reinterpret_cast<T *>(dX);
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int h = 2 * bh + a, w = 2 * bw + e;
+            if (h < H && w < W) dXv[(((long long)b * H + h) * W + w) * CV + cv] = out[a][e];
+        }
+}
+
+// NCHW: the same gather with the channel index fastest across a warp (coalesced dV reads), then a
+// shared-memory turn so that dX rows are written contiguously along W.
+template <bool MASK>
+__global__ void __launch_bounds__(256) imtrans_bwd_nchw_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                 float *__restrict__ dX, int B, int H, int W, int C, int nH, int nW)
+{
+    constexpr int OP = 2 * kTSEG + 1;  // 65: odd pitch per (c,a) row
+    __shared__ float O[kCCH * 2 * OP];
+    const int nseg = cdiv(nW, kTSEG);
+    int bx = blockIdx.x;
+    const int seg = bx % nseg; bx /= nseg;
+    const int bh = bx % nH;
+    const int b = bx / nH;
+    const int c0 = blockIdx.y * kCCH;
+    const int bw0 = seg * kTSEG;
+    const int tid = threadIdx.x;
+    const int c = tid & 31;
+    const long long plane = (long long)B * nH * nW * C;
+#pragma unroll 1
+    for (int it = 0; it < kTSEG / 8; ++it) {
+        const int bwl = (tid >> 5) + 8 * it;
+        const int bw = bw0 + bwl;
+        float out[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        if (bw < nW && c0 + c < C)
+            imtrans_bwd_block<float, MASK>(dV, Vm, plane, b, bh, bw, nH, nW, C, c0 + c, out);
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) O[(c * 2 + a) * OP + 2 * bwl + e] = out[a][e];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < kCCH * 2 * 2 * kTSEG; idx += 256) {
+        const int x = idx % (2 * kTSEG);
+        const int a = (idx / (2 * kTSEG)) & 1;
+        const int cc = idx / (4 * kTSEG);
+        const int h = 2 * bh + a, w = 2 * bw0 + x;
+        if (c0 + cc < C && h < H && w < W)
+            dX[(((long long)b * C + c0 + cc) * H + h) * W + w] = O[(cc * 2 + a) * OP + x];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, cudaStream_t st)
+{
+    if (!X || !V || B <= 0 || H <= 0 || W <= 0 || C <= 0) return WG2X2_ERR_BAD_ARG;
+    if (layout != WG2X2_NHWC && layout != WG2X2_NCHW) return WG2X2_ERR_BAD_ARG;
+    const int nH = (H + 1) / 2, nW = (W + 1) / 2;
+    if (layout == WG2X2_NHWC) {
+        if ((C % 4 == 0) && aligned16(X) && aligned16(V)) {
+            const long long total = (long long)B * nH * nW * (C / 4);
+            imtrans_fwd_nhwc_kernel<4><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+        } else {
+            const long long total = (long long)B * nH * nW * C;
+            imtrans_fwd_nhwc_kernel<1><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+        }
+    } else {
+        const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
+        if (gx > 0x7fffffffLL || cdiv(C, kCCH) > 65535) return WG2X2_ERR_UNSUPPORTED;
+        dim3 grid((unsigned)gx, cdiv(C, kCCH));
+        imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+    }
+    return launch_status();
+}
+
+int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W, int C, int layout, cudaStream_t st)
+{
+    if (!dV || !dX || B <= 0 || H <= 0 || W <= 0 || C <= 0) return WG2X2_ERR_BAD_ARG;
+    if (layout != WG2X2_NHWC && layout != WG2X2_NCHW) return WG2X2_ERR_BAD_ARG;
+    const int nH = (H + 1) / 2, nW = (W + 1) / 2;
+    if (layout == WG2X2_NHWC) {
+        const bool vec = (C % 4 == 0) && aligned16(dV) && aligned16(dX) && (!Vm || aligned16(Vm));
+        const long long total = (long long)B * nH * nW * (vec ? C / 4 : C);
+        const unsigned g = (unsigned)cdivll(total, 256);
+        if (vec) {
+            if (Vm) imtrans_bwd_nhwc_kernel<4, true><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+            else    imtrans_bwd_nhwc_kernel<4, false><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+        } else {
+            if (Vm) imtrans_bwd_nhwc_kernel<1, true><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+            else    imtrans_bwd_nhwc_kernel<1, false><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+        }
+    } else {
+        const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
+        if (gx > 0x7fffffffLL || cdiv(C, kCCH) > 65535) return WG2X2_ERR_UNSUPPORTED;
+        dim3 grid((unsigned)gx, cdiv(C, kCCH));
+        if (Vm) imtrans_bwd_nchw_kernel<true><<<grid, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+        else    imtrans_bwd_nchw_kernel<false><<<grid, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
+    }
+    return launch_status();
+}
+
+}  // namespace wg

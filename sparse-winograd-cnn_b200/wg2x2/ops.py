@@ -1,0 +1,131 @@
+"""Torch-facing calls into the C ABI: device memory and streams come from PyTorch, the
+arithmetic is entirely in libwinograd2x2_b200.so."""
+import torch
+
+from . import _lib
+from ._lib import MATH_FP32, MATH_TF32, NCHW, NHWC, lib
+
+_LAYOUTS = {"NHWC": NHWC, "NCHW": NCHW, NHWC: NHWC, NCHW: NCHW}
+_MATHS = {"fp32": MATH_FP32, "tf32": MATH_TF32, MATH_FP32: MATH_FP32, MATH_TF32: MATH_TF32}
+
+
+def _chk(t, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+        raise TypeError("%s must be a contiguous float32 CUDA tensor" % name)
+    return t
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _img_dims(x, layout):
+    if layout == NHWC:
+        B, H, W, C = x.shape
+    else:
+        B, C, H, W = x.shape
+    return B, H, W, C
+
+
+def _img_shape(B, H, W, C, layout):
+    return (B, H, W, C) if layout == NHWC else (B, C, H, W)
+
+
+def _workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device) if nbytes else None
+
+
+def imtrans_fwd(x, relu=False, layout="NHWC", out=None):
+    """x (B,H,W,C) or (B,C,H,W) -> V (16,B,nH,nW,C)."""
+    layout = _LAYOUTS[layout]
+    _chk(x, "x")
+    B, H, W, C = _img_dims(x, layout)
+    V = out if out is not None else torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_imtrans_fwd(_ptr(x), _ptr(V), B, H, W, C, layout, int(bool(relu)), _stream()), "wg2x2_imtrans_fwd")
+    return V
+
+
+def imtrans_bwd(dV, H, W, V_relu=None, layout="NHWC"):
+    """dV (16,B,nH,nW,C) -> dX; V_relu, if given, applies the ReLU mask V>0 first."""
+    layout = _LAYOUTS[layout]
+    _chk(dV, "dV")
+    _, B, nH, nW, C = dV.shape
+    if (H + 1) // 2 != nH or (W + 1) // 2 != nW:
+        raise ValueError("H, W do not match the tile grid of dV")
+    if V_relu is not None:
+        _chk(V_relu, "V_relu")
+    dX = torch.empty(_img_shape(B, H, W, C, layout), dtype=torch.float32, device=dV.device)
+    with torch.cuda.device(dV.device):
+        _lib.check(lib.wg2x2_imtrans_bwd(_ptr(dV), _ptr(V_relu), _ptr(dX), B, H, W, C, layout, _stream()), "wg2x2_imtrans_bwd")
+    return dX
+
+
+def conv_fwd(V, Wt, out_h=None, out_w=None, layout="NHWC", math="fp32", out=None, workspace=None):
+    """V (16,B,nH,nW,C), Wt (16,C,K) -> Y (B,out_h,out_w,K) / (B,K,out_h,out_w)."""
+    layout, math = _LAYOUTS[layout], _MATHS[math]
+    _chk(V, "V"); _chk(Wt, "Wt")
+    _, B, nH, nW, C = V.shape
+    K = Wt.shape[2]
+    if tuple(Wt.shape) != (16, C, K):
+        raise ValueError("Wt must be (16, C, K)")
+    out_h = 2 * nH if out_h is None else out_h
+    out_w = 2 * nW if out_w is None else out_w
+    Y = out if out is not None else torch.empty(_img_shape(B, out_h, out_w, K, layout), dtype=torch.float32, device=V.device)
+    nbytes = lib.wg2x2_conv_fwd_workspace_bytes(B, nH, nW, C, K, math)
+    ws = workspace if workspace is not None else _workspace(nbytes, V.device)
+    with torch.cuda.device(V.device):
+        _lib.check(lib.wg2x2_conv_fwd(_ptr(V), _ptr(Wt), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout, math,
+                                      _ptr(ws), ws.numel() if ws is not None else 0, _stream()), "wg2x2_conv_fwd")
+    return Y
+
+
+def conv_bwd(V, Wt, dY, mask=None, layout="NHWC", relu=False, math="fp32", need_dV=True, need_dW=True):
+    """Gradients (dV, dW) of conv_fwd for dY (B,H,W,K) / (B,K,H,W)."""
+    layout, math = _LAYOUTS[layout], _MATHS[math]
+    _chk(V, "V"); _chk(Wt, "Wt"); _chk(dY, "dY")
+    _, B, nH, nW, C = V.shape
+    K = Wt.shape[2]
+    Bd, H, W, Kd = _img_dims(dY, layout)
+    if (Bd, Kd) != (B, K) or (H + 1) // 2 != nH or (W + 1) // 2 != nW:
+        raise ValueError("dY does not match V / Wt")
+    if mask is not None:
+        _chk(mask, "mask")
+    dV = torch.empty_like(V) if need_dV else None
+    dW = torch.empty_like(Wt) if need_dW else None
+    nbytes = lib.wg2x2_conv_bwd_workspace_bytes(B, H, W, C, K, math, int(need_dW))
+    ws = _workspace(nbytes, V.device)
+    with torch.cuda.device(V.device):
+        _lib.check(lib.wg2x2_conv_bwd(_ptr(V), _ptr(Wt), _ptr(dY), _ptr(mask), _ptr(dV), _ptr(dW), B, H, W, C, K, layout,
+                                      int(bool(relu)), math, _ptr(ws), ws.numel() if ws is not None else 0, _stream()),
+                   "wg2x2_conv_bwd")
+    return dV, dW
+
+
+def layer_fwd(x, Wt, relu=True, layout="NHWC", math="fp32", keep_V=False, out=None, workspace=None):
+    """Whole Winograd-ReLU layer X -> Y (and V when keep_V)."""
+    layout, math = _LAYOUTS[layout], _MATHS[math]
+    _chk(x, "x"); _chk(Wt, "Wt")
+    B, H, W, C = _img_dims(x, layout)
+    K = Wt.shape[2]
+    if tuple(Wt.shape) != (16, C, K):
+        raise ValueError("Wt must be (16, C, K)")
+    Y = out if out is not None else torch.empty(_img_shape(B, H, W, K, layout), dtype=torch.float32, device=x.device)
+    V = torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device) if keep_V else None
+    nbytes = lib.wg2x2_layer_fwd_workspace_bytes(B, H, W, C, K, math, int(keep_V))
+    ws = workspace if workspace is not None else _workspace(nbytes, x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_layer_fwd(_ptr(x), _ptr(Wt), _ptr(Y), _ptr(V), B, H, W, C, K, layout, int(bool(relu)), math,
+                                       _ptr(ws), ws.numel() if ws is not None else 0, _stream()), "wg2x2_layer_fwd")
+    return (Y, V) if keep_V else Y
+
+
+def last_device_status():
+    import ctypes
+    where = ctypes.c_uint(0)
+    st = lib.wg2x2_last_device_status(_stream(), ctypes.byref(where))
+    return st, where.value
