@@ -79,6 +79,22 @@ int wg2x2_conv_fwd(const float *V, const float *Wt, float *Y, int B, int nH, int
 size_t wg2x2_conv_fwd_workspace_bytes(int B, int nH, int nW, int C, int K, int math);
 
 /*
+ * Weights prepared once for the tensor-core path, for callers whose weights do not change
+ * between calls (inference, or between optimiser steps): W (16,C,K) is repacked to (16,K,C),
+ * rounded to TF32 (round to nearest), and a map of all-zero 64x32 weight blocks is built so
+ * the kernel skips their loads and MMAs.  `prepared` is a caller-owned device buffer of
+ * wg2x2_prepared_weights_bytes(C,K) bytes, 256-byte aligned.  wg2x2_conv_fwd with
+ * WG2X2_MATH_TF32 does the same preparation into its workspace on every call.
+ * Takes the place of the per-step `W * mask` and of the operand set-up before
+ * cublasSgemmBatched (ResNet-18-var/winograd_conv.py:21-26, winograd2x2_conv_cuda.cu.cc:71-85).
+ * Needs C % 4 == 0 (WG2X2_ERR_UNSUPPORTED otherwise).
+ */
+size_t wg2x2_prepared_weights_bytes(int C, int K);
+int wg2x2_weights_prepare(const float *Wt, int C, int K, void *prepared, size_t prepared_bytes, void *stream);
+int wg2x2_conv_fwd_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K,
+                            int out_h, int out_w, int layout, void *stream);
+
+/*
  * Gradient of the product/output-transform op for dY of size (B,H,W,K):
  *   dV_t = (A dY A^T)_t . W_t^T   (skipped when dV == NULL)
  *   dW_t = V_t^T . (A dY A^T)_t   (skipped when dW == NULL), multiplied by mask when mask != NULL

@@ -20,6 +20,10 @@ size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K);
 int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW, int layout,
                 void *ws, size_t ws_bytes, cudaStream_t st);
 int tc_last_device_status(cudaStream_t st, unsigned int *where);
+size_t prepared_weights_bytes(int C, int K);
+int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
+int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
+                         int layout, cudaStream_t st);
 }  // namespace wg
 
 using namespace wg;
@@ -70,6 +74,24 @@ int wg2x2_conv_fwd(const float *V, const float *Wt, float *Y, int B, int nH, int
     if (math == WG2X2_MATH_TF32)
         return conv_fwd_tc(V, Wt, Y, B, nH, nW, C, K, out_h, out_w, layout, workspace, workspace_bytes, (cudaStream_t)stream);
     return conv_fwd_ffma(V, Wt, Y, B, nH, nW, C, K, out_h, out_w, layout, (cudaStream_t)stream);
+}
+
+size_t wg2x2_prepared_weights_bytes(int C, int K)
+{
+    return (C > 0 && K > 0) ? prepared_weights_bytes(C, K) : 0;
+}
+
+int wg2x2_weights_prepare(const float *Wt, int C, int K, void *prepared, size_t prepared_bytes, void *stream)
+{
+    return weights_prepare(Wt, C, K, prepared, prepared_bytes, (cudaStream_t)stream);
+}
+
+int wg2x2_conv_fwd_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int out_h,
+                            int out_w, int layout, void *stream)
+{
+    if (!V || !prepared || !Y || B <= 0 || nH <= 0 || nW <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!layout_ok(layout) || !crop_ok(out_h, nH) || !crop_ok(out_w, nW)) return WG2X2_ERR_BAD_ARG;
+    return conv_fwd_tc_prepared(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, (cudaStream_t)stream);
 }
 
 size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int want_dW)

@@ -1,9 +1,499 @@
+// TF32 tensor-core path of the Winograd-domain product (sm_100a only): tcgen05.mma with
+// accumulators in TMEM, operands staged by TMA into 128B-swizzled shared memory, the
+// A^T m A output transform done by the epilogue warps straight from TMEM.
+//
+// Work unit = 128 tiles (one TMEM lane per tile) x 64 output channels x all 16 Winograd
+// positions.  The 16 positions are walked one Winograd row i (four positions j) at a time:
+// four 128x64 fp32 accumulators (256 TMEM columns) per row, double-buffered across rows
+// (512 columns), so the epilogue of row i overlaps the MMAs of row i+1 and V is read from
+// memory exactly once per 64 output channels.  Nothing but Y is written.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..9 = epilogue (two warps per TMEM lane quarter, 32 columns each).
+// Every mbarrier wait is bounded; on expiry the kernel records where it gave up, drains
+// and returns (status readable through wg2x2_last_device_status).
+#include <cuda.h>
+
 #include "wg_common.cuh"
+
 namespace wg {
-size_t conv_fwd_tc_workspace_bytes(int, int, int, int, int) { return 0; }
-int conv_fwd_tc(const float *, const float *, float *, int, int, int, int, int, int, int, int, void *, size_t, cudaStream_t)
+
+constexpr int kBlockM = 128;            // tiles per unit (TMEM lanes)
+constexpr int kBlockN = 64;             // output channels per unit
+constexpr int kBlockK = 32;             // tf32 elements per stage along C: 128 bytes = one swizzle row
+constexpr int kStages = 8;
+constexpr int kABytes = kBlockM * kBlockK * 4;   // 16 KB
+constexpr int kBBytes = kBlockN * kBlockK * 4;   //  8 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTcThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr long long kSpinLimit = 40LL * 1000 * 1000;  // try_wait polls before a wait gives up (~ a second)
+
+__device__ unsigned int g_tc_status[2];  // [0] = 0 ok / 1 timeout, [1] = where (role<<8 | detail)
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    return WG2X2_ERR_UNSUPPORTED;
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-int tc_last_device_status(cudaStream_t, unsigned int *where) { if (where) *where = 0; return WG2X2_OK; }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (or when another role already did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where)
+{
+    for (long long it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023) == 1023 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    g_tc_status[1] = where;
+    g_tc_status[0] = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], M=128, N=kBlockN, K=8 (tf32)
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// mbarrier arrives once all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns -> 8 registers per thread
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&r)[8])
+{
+    uint32_t u[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+                 : "r"(taddr));
+#pragma unroll
+    for (int q = 0; q < 8; ++q) r[q] = __uint_as_float(u[q]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart,
+// 8-row groups 1024 B apart (SBO), LBO unused (1), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D=f32, A=B=tf32, both K-major, N and M as given
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------------
+// Weight preparation: W (16,C,K) -> Wp (16,K,C) rounded to TF32 (round-to-nearest), plus a
+// byte map flag[t][kb][cc] = 1 when the 64x32 block (out-channels kb*64.., in-channels cc*32..)
+// of position t has any non-zero weight.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restrict__ Wt, float *__restrict__ Wp,
+                                                             unsigned char *__restrict__ flags, int C, int K, int nKB, int nCC)
+{
+    __shared__ float tile[32][33];
+    __shared__ int any;
+    const int t = blockIdx.z;
+    const int c0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    if (threadIdx.x == 0) any = 0;
+    __syncthreads();
+    int nz = 0;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int c = c0 + ty + 8 * r, k = k0 + tx;
+        float w = 0.f;
+        if (c < C && k < K) w = __ldg(Wt + ((long long)t * C + c) * K + k);
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(w));
+        w = __uint_as_float(u);
+        nz |= (w != 0.f);
+        tile[ty + 8 * r][tx] = w;
+    }
+    if (nz) any = 1;
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int k = k0 + ty + 8 * r, c = c0 + tx;
+        if (c < C && k < K) Wp[((long long)t * K + k) * C + c] = tile[tx][ty + 8 * r];
+    }
+    if (threadIdx.x == 0 && any) flags[((long long)t * nKB + (k0 / kBlockN)) * nCC + (c0 / kBlockK)] = 1;
+}
+
+// ---------------------------------------------------------------------------------------
+// Main kernel
+// ---------------------------------------------------------------------------------------
+struct TcParams {
+    float *Y;
+    const unsigned char *flags;
+    long long P;
+    int nH, nW, C, K, outH, outW;
+    int nMT, nKB, nCC;   // m-tiles, 64-channel blocks, 32-channel chunks
+    int units;
+};
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams prm)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // 1024-B aligned operand stages
+    uint8_t *gen_base = smem_raw + (base - raw);
+    const uint32_t bars = base + kStages * kStageBytes;           // barrier block
+    uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kStages * kStageBytes);
+    // barrier layout (8 B each): full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr, abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kStages + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * kStages + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * kStages + 2 + b); };
+    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + 2 * kStages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kStages + 5);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void *)tmem_ptr_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_ptr_slot;
+
+    const int nCC = prm.nCC;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------------
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
+                const int mt = u / prm.nKB, kb = u % prm.nKB;
+                const int p0 = mt * kBlockM, k0 = kb * kBlockN;
+                for (int t = 0; t < 16 && ok; ++t) {
+                    const unsigned char *fl = prm.flags + ((long long)t * prm.nKB + kb) * nCC;
+                    for (int cc = 0; cc < nCC; ++cc) {
+                        if (cc > 0 && !fl[cc]) continue;   // all-zero weight block: nothing to add
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x100u | s)) { ok = false; break; }
+                        mbar_expect_tx(full_bar(s), kStageBytes);
+                        const uint32_t a_dst = base + s * kStageBytes;
+                        tma_load_3d(a_dst, &mapA, full_bar(s), cc * kBlockK, p0, t);
+                        tma_load_3d(a_dst + kABytes, &mapB, full_bar(s), cc * kBlockK, k0, t);
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) {
+                // give copies already in flight about a millisecond to land before the CTA
+                // hands its shared memory back
+                for (int it = 0; it < 1000; ++it) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(kBlockM, kBlockN);
+            int s = 0; uint32_t ph = 0;
+            uint32_t acc_use[2] = {0, 0};
+            bool ok = true;
+            for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
+                const int kb = u % prm.nKB;
+                for (int i = 0; i < 4 && ok; ++i) {
+                    const int buf = i & 1;
+                    // the epilogue must have drained this accumulator buffer
+                    if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf)) { ok = false; break; }
+                    acc_use[buf]++;
+                    tc_fence_after();
+                    for (int j = 0; j < 4 && ok; ++j) {
+                        const int t = 4 * i + j;
+                        const unsigned char *fl = prm.flags + ((long long)t * prm.nKB + kb) * nCC;
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 4 * kBlockN + j * kBlockN);
+                        for (int cc = 0; cc < nCC; ++cc) {
+                            if (cc > 0 && !fl[cc]) continue;
+                            if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s)) { ok = false; break; }
+                            tc_fence_after();
+                            const uint32_t a_addr = base + s * kStageBytes;
+                            const uint64_t adesc = make_desc_k_sw128(a_addr);
+                            const uint64_t bdesc = make_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+                            for (int kk = 0; kk < kBlockK / 8; ++kk)   // 32 bytes (8 tf32) further along K per step
+                                umma_tf32(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (cc > 0 || kk > 0) ? 1u : 0u);
+                            umma_commit(empty_bar(s));
+                            if (++s == kStages) { s = 0; ph ^= 1u; }
+                        }
+                    }
+                    if (ok) umma_commit(accf_bar(buf));
+                }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------------
+        const int ew = warp - 2;
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int half = ew >> 2;          // which 32 of the 64 columns
+        uint32_t acc_use[2] = {0, 0};
+        bool ok = true;
+        for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
+            const int mt = u / prm.nKB, kb = u % prm.nKB;
+            float y[4][32];                // [2a+e][column]
+#pragma unroll
+            for (int o = 0; o < 4; ++o)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) y[o][c] = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int buf = i & 1;
+                if (ok && !mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
+                acc_use[buf]++;
+                if (ok) {
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 4 * kBlockN + half * 32);
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        float m[4][8];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tmem_ld8(taddr + (uint32_t)(j * kBlockN + ch * 8), m[j]);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            float z0, z1;
+                            at_cols(m[0][c], m[1][c], m[2][c], m[3][c], z0, z1);
+                            // rows: AT[0] = [1,1,1,0], AT[1] = [0,1,-1,-1]
+                            if (i <= 2) { y[0][ch * 8 + c] += z0; y[1][ch * 8 + c] += z1; }
+                            if (i == 1) { y[2][ch * 8 + c] += z0; y[3][ch * 8 + c] += z1; }
+                            if (i >= 2) { y[2][ch * 8 + c] -= z0; y[3][ch * 8 + c] -= z1; }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acce_bar(buf));
+                }
+            }
+            if (!ok) break;
+            // ---- store the 2x2 outputs of this thread's tile for its 32 channels ----
+            const long long p = (long long)mt * kBlockM + q * 32 + lane;
+            if (p < prm.P) {
+                const int tw = (int)(p % prm.nW), th = (int)((p / prm.nW) % prm.nH), b = (int)(p / ((long long)prm.nW * prm.nH));
+                const int kbase = kb * kBlockN + half * 32;
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int h = 2 * th + a, w = 2 * tw + e;
+                        if (h >= prm.outH || w >= prm.outW) continue;
+                        if (LAYOUT == WG2X2_NHWC) {
+                            float *dst = prm.Y + (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase;
+                            if (kbase + 32 <= prm.K && (prm.K & 3) == 0) {
+#pragma unroll
+                                for (int c = 0; c < 32; c += 4)
+                                    *reinterpret_cast<float4 *>(dst + c) = make_float4(y[2 * a + e][c], y[2 * a + e][c + 1], y[2 * a + e][c + 2], y[2 * a + e][c + 3]);
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < 32; ++c)
+                                    if (kbase + c < prm.K) dst[c] = y[2 * a + e][c];
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (kbase + c < prm.K)
+                                    prm.Y[(((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + w] = y[2 * a + e][c];
+                        }
+                    }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 3-D map over a (16, rows, C) fp32 tensor, C contiguous: box = 32 x box_rows x 1, 128-B swizzle,
+// out-of-range elements read as zero.
+static bool make_map(CUtensorMap *map, const float *ptr, int C, long long rows, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)rows, 16};
+    cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)rows * C * 4};
+    cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+size_t prepared_weights_bytes(int C, int K)
+{
+    const size_t w = align_up((size_t)16 * K * C * sizeof(float), 256);
+    const size_t f = align_up((size_t)16 * cdiv(K, kBlockN) * cdiv(C, kBlockK), 256);
+    return w + f;
+}
+
+bool tc_shape_supported(int C, int K) { return C % 4 == 0 && C >= 4 && K >= 1; }
+
+int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st)
+{
+    if (!Wt || !prepared || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!tc_shape_supported(C, K)) return WG2X2_ERR_UNSUPPORTED;
+    if (bytes < prepared_weights_bytes(C, K)) return WG2X2_ERR_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(prepared) & 255u) return WG2X2_ERR_BAD_ARG;
+    const int nKB = cdiv(K, kBlockN), nCC = cdiv(C, kBlockK);
+    float *Wp = static_cast<float *>(prepared);
+    unsigned char *flags = static_cast<unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256);
+    if (cudaMemsetAsync(flags, 0, (size_t)16 * nKB * nCC, st) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    dim3 grid(cdiv(K, 32), cdiv(C, 32), 16);
+    pack_weights_kernel<<<grid, 256, 0, st>>>(Wt, Wp, flags, C, K, nKB, nCC);
+    return launch_status();
+}
+
+int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
+                         int layout, cudaStream_t st)
+{
+    if (!V || !prepared || !Y) return WG2X2_ERR_BAD_ARG;
+    if (!tc_shape_supported(C, K)) return WG2X2_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(V) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 15u)) return WG2X2_ERR_BAD_ARG;
+    const long long P = (long long)B * nH * nW;
+    if (P > 0x7fffffffLL - kBlockM) return WG2X2_ERR_UNSUPPORTED;
+    TcParams prm;
+    prm.Y = Y;
+    prm.P = P; prm.nH = nH; prm.nW = nW; prm.C = C; prm.K = K; prm.outH = outH; prm.outW = outW;
+    prm.nMT = (int)cdivll(P, kBlockM);
+    prm.nKB = cdiv(K, kBlockN);
+    prm.nCC = cdiv(C, kBlockK);
+    prm.units = prm.nMT * prm.nKB;
+    prm.flags = static_cast<const unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256);
+    CUtensorMap mapA, mapB;
+    if (!make_map(&mapA, V, C, P, kBlockM)) return WG2X2_ERR_LAUNCH;
+    if (!make_map(&mapB, static_cast<const float *>(prepared), C, K, kBlockN)) return WG2X2_ERR_LAUNCH;
+    const cudaError_t e = layout == WG2X2_NHWC
+        ? cudaFuncSetAttribute(conv_fwd_tc_kernel<WG2X2_NHWC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
+        : cudaFuncSetAttribute(conv_fwd_tc_kernel<WG2X2_NCHW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
+    if (layout == WG2X2_NHWC) conv_fwd_tc_kernel<WG2X2_NHWC><<<grid, kTcThreads, kSmemBytes, st>>>(mapA, mapB, prm);
+    else                      conv_fwd_tc_kernel<WG2X2_NCHW><<<grid, kTcThreads, kSmemBytes, st>>>(mapA, mapB, prm);
+    return launch_status();
+}
+
+size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K)
+{
+    (void)B; (void)nH; (void)nW;
+    if (C <= 0 || K <= 0) return 0;
+    return prepared_weights_bytes(C, K);
+}
+
+int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW, int layout,
+                void *ws, size_t ws_bytes, cudaStream_t st)
+{
+    if (!tc_shape_supported(C, K)) return WG2X2_ERR_UNSUPPORTED;
+    if (!ws || ws_bytes < prepared_weights_bytes(C, K)) return WG2X2_ERR_WORKSPACE;
+    const int s = weights_prepare(Wt, C, K, ws, ws_bytes, st);
+    if (s != WG2X2_OK) return s;
+    return conv_fwd_tc_prepared(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, st);
+}
+
+int tc_last_device_status(cudaStream_t st, unsigned int *where)
+{
+    if (cudaStreamSynchronize(st) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    unsigned int h[2] = {0, 0};
+    if (cudaMemcpyFromSymbol(h, g_tc_status, sizeof(h)) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    if (where) *where = h[1];
+    if (h[0]) {
+        const unsigned int z[2] = {0, 0};
+        cudaMemcpyToSymbol(g_tc_status, z, sizeof(z));
+        return WG2X2_ERR_TIMEOUT;
+    }
+    return WG2X2_OK;
+}
+
+}  // namespace wg

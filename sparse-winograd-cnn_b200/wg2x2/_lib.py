@@ -36,6 +36,9 @@ _SIGS = {
     "wg2x2_imtrans_bwd": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "wg2x2_conv_fwd": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i]),
+    "wg2x2_prepared_weights_bytes": (_z, [_i, _i]),
+    "wg2x2_weights_prepare": (_i, [_p, _i, _i, _p, _z, _p]),
+    "wg2x2_conv_fwd_prepared": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "wg2x2_conv_bwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_layer_fwd": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),

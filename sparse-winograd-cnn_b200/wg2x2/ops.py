@@ -84,6 +84,32 @@ def conv_fwd(V, Wt, out_h=None, out_w=None, layout="NHWC", math="fp32", out=None
     return Y
 
 
+def prepare_weights(Wt):
+    """Wt (16,C,K) -> opaque device buffer for conv_fwd_prepared (TF32 tensor-core path)."""
+    _chk(Wt, "Wt")
+    _, C, K = Wt.shape
+    n = lib.wg2x2_prepared_weights_bytes(C, K)
+    buf = torch.empty(n, dtype=torch.uint8, device=Wt.device)
+    with torch.cuda.device(Wt.device):
+        _lib.check(lib.wg2x2_weights_prepare(_ptr(Wt), C, K, _ptr(buf), n, _stream()), "wg2x2_weights_prepare")
+    buf._wg_ck = (C, K)
+    return buf
+
+
+def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out=None):
+    """As conv_fwd(math="tf32") with weights already prepared by prepare_weights."""
+    layout = _LAYOUTS[layout]
+    _chk(V, "V")
+    _, B, nH, nW, C = V.shape
+    out_h = 2 * nH if out_h is None else out_h
+    out_w = 2 * nW if out_w is None else out_w
+    Y = out if out is not None else torch.empty(_img_shape(B, out_h, out_w, K, layout), dtype=torch.float32, device=V.device)
+    with torch.cuda.device(V.device):
+        _lib.check(lib.wg2x2_conv_fwd_prepared(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
+                                               _stream()), "wg2x2_conv_fwd_prepared")
+    return Y
+
+
 def conv_bwd(V, Wt, dY, mask=None, layout="NHWC", relu=False, math="fp32", need_dV=True, need_dW=True):
     """Gradients (dV, dW) of conv_fwd for dY (B,H,W,K) / (B,K,H,W)."""
     layout, math = _LAYOUTS[layout], _MATHS[math]

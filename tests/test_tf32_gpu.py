@@ -1,0 +1,119 @@
+"""GPU parity of the tcgen05 TF32 path against the float64 oracle.  Tolerance 5e-3 on
+max|a-b| / max|b| (TF32 keeps 10 mantissa bits per operand; accumulation is fp32 in TMEM)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL_TF32 = 5e-3
+
+SHAPES = [  # B, H, W, C, K
+    (2, 14, 14, 64, 64),      # one partial m-tile
+    (4, 56, 56, 64, 64),      # BASELINE config 1
+    (3, 6, 6, 32, 32), (3, 6, 6, 32, 64),
+    (2, 7, 7, 64, 128),       # odd size, two channel blocks
+    (1, 28, 28, 128, 96),     # K not a multiple of 64
+    (2, 9, 13, 36, 20),       # C not a multiple of 32, K < 64
+    (3, 14, 14, 256, 256),    # conv4_x shape
+    (1, 30, 34, 8, 8),
+]
+
+
+@pytest.fixture(scope="module")
+def wg():
+    import wg2x2
+    return wg2x2
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+
+
+def _inputs(shape, density=1.0):
+    B, H, W, C, K = shape
+    rng = np.random.default_rng(sum(shape))
+    X = rng.standard_normal((B, H, W, C)).astype(np.float32)
+    Wt = (0.05 * rng.standard_normal((16, C, K))).astype(np.float32)
+    if density < 1.0:
+        Wt *= (rng.random((16, C, K)) < density)
+    return X, Wt.astype(np.float32)
+
+
+def _status_ok(wg):
+    st, where = wg.last_device_status()
+    assert st == 0, "device-side wait gave up at 0x%x" % where
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_conv_fwd_tf32(wg, oracle, shape, layout):
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    Y = wg.conv_fwd(_dev(V), _dev(Wt), H, W, layout=layout, math="tf32")
+    _status_ok(wg)
+    got = Y.cpu().numpy()
+    if layout == "NCHW":
+        got = np.transpose(got, (0, 2, 3, 1))
+    want = oracle.conv_fwd(V, Wt, H, W)
+    assert np.isfinite(got).all()
+    err = oracle.max_rel(got, want)
+    assert err <= TOL_TF32, "max_rel %.3g" % err
+    assert oracle.rel_l1(got, want) <= TOL_TF32
+
+
+def test_tf32_matches_fp32_path_closely(wg, oracle):
+    """Same inputs through both math modes: they differ only by TF32 rounding."""
+    shape = (4, 56, 56, 64, 64)
+    X, Wt = _inputs(shape)
+    x, wt = _dev(X), _dev(Wt)
+    y32 = wg.layer_fwd(x, wt, relu=True, math="fp32")
+    ytf = wg.layer_fwd(x, wt, relu=True, math="tf32")
+    _status_ok(wg)
+    assert oracle.max_rel(ytf.cpu().numpy(), y32.cpu().numpy()) <= TOL_TF32
+    assert not torch.equal(y32, ytf)   # the tensor-core path really ran
+
+
+def test_pruned_weights_and_block_skipping(wg, oracle):
+    """Unstructured mask (density 0.3, as in BASELINE config 3) and a block-structured mask whose
+    all-zero 64x32 blocks are skipped by the kernel: both must equal the dense arithmetic."""
+    shape = (2, 14, 14, 256, 256)
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape, density=0.3)
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    Y = wg.conv_fwd(_dev(V), _dev(Wt), H, W, math="tf32").cpu().numpy()
+    assert oracle.max_rel(Y, oracle.conv_fwd(V, Wt, H, W)) <= TOL_TF32
+    rng = np.random.default_rng(9)
+    blocks = rng.random((16, C // 32, K // 64)) < 0.4
+    blocks[:, 0, :] |= rng.random((16, K // 64)) < 0.5    # some first chunks empty as well
+    Wb = Wt * np.repeat(np.repeat(blocks, 32, axis=1), 64, axis=2)
+    prepared = wg.prepare_weights(_dev(Wb))
+    Yb = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W).cpu().numpy()
+    _status_ok(wg)
+    assert oracle.max_rel(Yb, oracle.conv_fwd(V, Wb, H, W)) <= TOL_TF32
+    # all-zero weights: the output must be exactly zero, not stale accumulator contents
+    Yz = wg.conv_fwd(_dev(V), _dev(np.zeros_like(Wt)), H, W, math="tf32")
+    assert float(Yz.abs().max()) == 0.0
+
+
+def test_prepared_weights_reused(wg, oracle):
+    shape = (2, 28, 28, 128, 128)
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    prepared = wg.prepare_weights(_dev(Wt))
+    V = wg.imtrans_fwd(_dev(X), relu=True)
+    Y1 = wg.conv_fwd_prepared(V, prepared, K, H, W)
+    Y2 = wg.conv_fwd_prepared(V, prepared, K, H, W)
+    assert torch.equal(Y1, Y2)
+    want = oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)
+    assert oracle.max_rel(Y1.cpu().numpy(), want) <= TOL_TF32
+
+
+def test_unsupported_shape_reports(wg):
+    """C % 4 != 0 cannot be described to TMA: the TF32 mode says so instead of falling back."""
+    V = torch.zeros((16, 1, 2, 2, 6), device="cuda")
+    Wt = torch.zeros((16, 6, 8), device="cuda")
+    with pytest.raises(wg.Wg2x2Error) as e:
+        wg.conv_fwd(V, Wt, math="tf32")
+    assert e.value.status == -5
