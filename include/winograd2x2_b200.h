@@ -110,6 +110,25 @@ int wg2x2_conv_bwd(const float *V, const float *Wt, const float *dY, const float
 size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int want_dW);
 
 /*
+ * dW of wg2x2_conv_bwd (FP32 path) for callers that cannot allocate device memory: hooks
+ * that receive only an op's inputs and outputs, processes that forbid cudaMalloc after
+ * start-up, plug-ins of a host application that owns all device memory.  The split-P
+ * partial sums go to a fixed 32 MiB array inside the library (held by every GPU that loads
+ * it, until exit) instead of a caller workspace.  No counterpart in the reference, whose
+ * caller always allocates the temporaries.
+ *  - Limit: splits * 16*C*K floats <= wg2x2_conv_bwd_dw_noalloc_max_bytes()/4, with the same
+ *    split count as wg2x2_conv_bwd; larger problems return WG2X2_ERR_WORKSPACE.
+ *  - The first call on each device looks up the array's device address; make that call
+ *    before any stream capture.  The call itself allocates nothing.
+ *  - Every call shares the one array: calls that overlap on the GPU (two streams, two
+ *    threads) race.  Nothing in it needs clearing: each call overwrites all it later reads.
+ * Arguments as in wg2x2_conv_bwd; the result equals its dW bit for bit.
+ */
+int wg2x2_conv_bwd_dw_noalloc(const float *V, const float *dY, const float *mask, float *dW, int B, int H,
+                              int W, int C, int K, int layout, void *stream);
+size_t wg2x2_conv_bwd_dw_noalloc_max_bytes(void);
+
+/*
  * Whole layer forward, X -> Y = conv(relu?(imtrans(X)), W): the call pair at
  * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119.  V_out, when not NULL, receives
  * the transformed (post-ReLU) input for a later backward pass; when NULL it lives in the

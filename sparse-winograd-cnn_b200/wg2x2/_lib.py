@@ -41,6 +41,8 @@ _SIGS = {
     "wg2x2_conv_fwd_prepared": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "wg2x2_conv_bwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
+    "wg2x2_conv_bwd_dw_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "wg2x2_conv_bwd_dw_noalloc_max_bytes": (_z, []),
     "wg2x2_layer_fwd": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_layer_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_last_device_status": (_i, [_p, ctypes.POINTER(ctypes.c_uint)]),
