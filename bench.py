@@ -157,6 +157,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
+    ap.add_argument("--e2e-chunks", type=int, default=4, help="chunks of the host-buffer pipeline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -245,15 +246,12 @@ def main():
     # ---- end to end through the public call with host buffers ------------------------------
     Xpin = torch.from_numpy(Xh).pin_memory()
     Ypin = torch.empty(Y.shape, dtype=torch.float32).pin_memory()
-    Xd = torch.empty_like(Xs[0])
-    lws_n = wg2x2._lib.lib.wg2x2_layer_fwd_workspace_bytes(B, H, W, C, K, wg2x2.ops._MATHS[args.math], 0)
-    lws = torch.empty(max(lws_n, 1), dtype=torch.uint8, device=dev)
-    e2e_steps = max(3, min(args.steps, 10))
+    # the public host-buffer call: chunked, copies and kernels overlapped on three streams
+    pipe = wg2x2.HostLayerPipeline(B, H, W, C, K, layout=args.layout, math=args.math, relu=True, chunks=args.e2e_chunks)
+    e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step():
-        Xd.copy_(Xpin, non_blocking=True)
-        wg2x2.layer_fwd(Xd, Wt, relu=True, layout=args.layout, math=args.math, out=Y, workspace=lws)
-        Ypin.copy_(Y, non_blocking=True)
+        pipe(Xpin, Wt, Ypin)
 
     for _ in range(2):
         e2e_step()
@@ -308,7 +306,8 @@ def main():
         "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
         "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
                    "l2": "4 rotating input buffers; %.0f MB moved per step" % ((k1_bytes + k2_bytes) / 1e6),
-                   "weights": "prepared once outside the timed region (wg2x2_weights_prepare); e2e repacks per call"},
+                   "weights": "prepared once outside the timed region (wg2x2_weights_prepare)",
+                   "e2e": "wg2x2.HostLayerPipeline: pinned host X -> Y, %d chunks, H2D / kernels / D2H on three streams" % args.e2e_chunks},
         "layer_gbs_two_kernel": (k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
         "layer_tflops": flops * world / (ms_step * 1e-3) / 1e12,
         "roofline": roof, "clocks": clocks,

@@ -1,0 +1,72 @@
+"""Layer forward for batches that live in host memory: the batch is cut into chunks and the
+host-to-device copy of chunk i+1, the kernels of chunk i and the device-to-host copy of chunk i-1
+run on three CUDA streams, so that the PCIe link is busy in both directions while the GPU works."""
+import torch
+
+from . import ops
+
+
+class HostLayerPipeline:
+    def __init__(self, B, H, W, C, K, layout="NHWC", math="tf32", relu=True, chunks=4, device=None):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.B, self.H, self.W, self.C, self.K = B, H, W, C, K
+        self.layout, self.math, self.relu = layout, math, relu
+        chunks = max(1, min(chunks, B))
+        base, extra = divmod(B, chunks)
+        self.bounds, lo = [], 0
+        for i in range(chunks):
+            hi = lo + base + (1 if i < extra else 0)
+            self.bounds.append((lo, hi))
+            lo = hi
+        nH, nW = (H + 1) // 2, (W + 1) // 2
+        in_shape = (lambda n: (n, H, W, C)) if layout == "NHWC" else (lambda n: (n, C, H, W))
+        out_shape = (lambda n: (n, H, W, K)) if layout == "NHWC" else (lambda n: (n, K, H, W))
+        with torch.cuda.device(self.device):
+            self.xd = [torch.empty(in_shape(hi - lo), device=self.device) for lo, hi in self.bounds]
+            self.yd = [torch.empty(out_shape(hi - lo), device=self.device) for lo, hi in self.bounds]
+            biggest = max(hi - lo for lo, hi in self.bounds)
+            self.vflat = [torch.empty(16 * biggest * nH * nW * C, device=self.device) for _ in range(2)]
+            self.vshape = lambda n: (16, n, nH, nW, C)
+            self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+            self.ev_in = [torch.cuda.Event() for _ in self.bounds]
+            self.ev_run = [torch.cuda.Event() for _ in self.bounds]
+        self._prepared, self._prepared_for = None, None
+
+    def _weights(self, Wt):
+        if self.math != "tf32":
+            return None
+        key = (Wt.data_ptr(), Wt._version)
+        if self._prepared_for != key:
+            self._prepared = ops.prepare_weights(Wt)
+            self._prepared_for = key
+        return self._prepared
+
+    def __call__(self, x_host, Wt, y_host):
+        """x_host, y_host: pinned host tensors of the full batch; returns y_host (complete on return of
+        `torch.cuda.current_stream().synchronize()` -- the caller's stream waits for the last copy)."""
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(cur)
+        with torch.cuda.stream(self.s_run):
+            prepared = self._weights(Wt)
+        for i, (lo, hi) in enumerate(self.bounds):
+            with torch.cuda.stream(self.s_in):
+                self.xd[i].copy_(x_host[lo:hi], non_blocking=True)
+                self.ev_in[i].record()
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.ev_in[i])
+                shape = self.vshape(hi - lo)
+                v = self.vflat[i % 2][:shape[0] * shape[1] * shape[2] * shape[3] * shape[4]].view(shape)
+                ops.imtrans_fwd(self.xd[i], relu=self.relu, layout=self.layout, out=v)
+                if prepared is not None:
+                    ops.conv_fwd_prepared(v, prepared, self.K, self.H, self.W, layout=self.layout, out=self.yd[i])
+                else:
+                    ops.conv_fwd(v, Wt, self.H, self.W, layout=self.layout, math=self.math, out=self.yd[i])
+                self.ev_run[i].record()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_run[i])
+                y_host[lo:hi].copy_(self.yd[i], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_in)
+        cur.wait_stream(self.s_run)
+        return y_host

@@ -299,3 +299,23 @@ def test_determinism_and_canaries(wg):
         results.append([t.clone() for t in (V, Y, dV, dW, dX)])
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_host_pipeline_equals_resident_call(wg, oracle, layout):
+    """The chunked host-buffer pipeline gives the bits of the one-shot device call, on repeated use."""
+    B, H, W, C, K = 10, 14, 14, 32, 64
+    X, Wt, _, _ = _inputs((B, H, W, C, K))
+    xl = _to_layout(X, layout)
+    want = wg.layer_fwd(_dev(xl), _dev(Wt), relu=True, layout=layout, math="tf32")
+    pipe = wg.HostLayerPipeline(B, H, W, C, K, layout=layout, math="tf32", chunks=4)
+    xh = torch.from_numpy(np.ascontiguousarray(xl)).pin_memory()
+    yh = torch.empty(tuple(want.shape)).pin_memory()
+    wt = _dev(Wt)
+    for _ in range(3):
+        yh.zero_()
+        pipe(xh, wt, yh)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(yh, want.cpu())
+    _check(_from_layout(yh, layout), oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W), tol=5e-3, tol_l1=5e-3,
+           what="pipeline vs oracle")
