@@ -97,6 +97,7 @@ class ClockSampler:
 def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
     """Images per second of the C oracle (float32, OpenMP over all host cores) on a batch slice."""
     from oracle import wg_oracle as o
+    cores = o.set_threads()
     b = sample_b or max(1, min(wl["B"], 4))
     X, Wt = make_inputs(dict(wl, B=b))
     Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
@@ -111,7 +112,6 @@ def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
         dt = time.perf_counter() - t0
         if dt > seconds:
             break
-    cores = len(os.sched_getaffinity(0))
     return dict(value=b * n / dt, unit=UNIT, cores=cores, kind="port",
                 sample="batch slice of %d images of the %dx%dx%dx%d layer, %d passes in %.1f s, float32 C restatement with OpenMP"
                        % (b, wl["C"], wl["K"], wl["H"], wl["W"], n, dt)), b, dt / n
@@ -121,6 +121,7 @@ def run_reference(args, wl, rank, world):
     if rank != 0:
         return
     from oracle import wg_oracle as o
+    cores = o.set_threads()
     b = max(1, min(wl["B"], 4))
     X, Wt = make_inputs(dict(wl, B=b))
     Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
@@ -134,7 +135,6 @@ def run_reference(args, wl, rank, world):
         o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
     dt = time.perf_counter() - t0
     val = b * args.steps / dt
-    cores = len(os.sched_getaffinity(0))
     sample = "each step = batch slice of %d images of the workload (host cores, OpenMP, float32)" % b
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,

@@ -13,7 +13,7 @@
  * (winograd2x2_cublas/winograd2x2_conv/winograd2x2_conv_grad_test.py:205-227,
  *  winograd2x2_cublas/winograd2x2_imTrans/winograd2x2_imTrans_grad_test.py:194-216), and
  * (c) against outputs of the reference's own CUDA kernels compiled unmodified for
- * sm_100a (oracle/build_ref.sh) and run on a B200; those outputs are the fixtures under
+ * sm_100a (oracle/Makefile, target "ref") and run on a B200; those outputs are the fixtures under
  * tests/golden/.
  *
  * Layouts are the reference's: X (B,H,W,C); V (16,B,nH,nW,C); W (16,C,K);
@@ -21,6 +21,7 @@
  *
  * The file is compiled twice: -DREAL=float -DSUF=_f32 and -DREAL=double -DSUF=_f64.
  */
+#include <omp.h>
 #include <stddef.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -33,6 +34,16 @@
 #define CAT_(a, b) a##b
 #define CAT(a, b) CAT_(a, b)
 #define FN(name) CAT(name, SUF)
+
+#ifndef WGO_THREADS_DEFINED
+#define WGO_THREADS_DEFINED
+/* Number of OpenMP threads the loops below use (launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1, which would silently turn the timed CPU baseline into a one-core run). */
+#if defined(WGO_EXPORT_THREADS)
+void wgo_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int wgo_get_max_threads(void) { return omp_get_max_threads(); }
+#endif
+#endif
 
 /* B^T of F(2x2,3x3); the 16 sums at
  * winograd2x2_cublas/winograd2x2_imTrans/winograd2x2_imTrans_cuda.cu.cc:112-127

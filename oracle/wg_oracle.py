@@ -39,6 +39,13 @@ def lib():
     return _LIB
 
 
+def set_threads(n=None):
+    """Use n OpenMP threads (default: every core this process may run on); returns the count in effect."""
+    n = len(os.sched_getaffinity(0)) if n is None else int(n)
+    lib().wgo_set_threads(n)
+    return int(lib().wgo_get_max_threads())
+
+
 def _suf(dtype):
     dtype = np.dtype(dtype)
     if dtype == np.float32:
