@@ -147,6 +147,85 @@ def run_reference(args, wl, rank, world):
     }))
 
 
+def run_resnet(args, rank, world, local):
+    """BASELINE config 4: ResNet-18-var forward, batch 256 in total, sharded over the ranks (strong scaling)."""
+    import torch
+    import torch.distributed as dist
+    import wg2x2  # noqa: F401
+    from resnet18_var import ResNet18Var
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    total = args.batch if args.batch > 0 else 256
+    lo, hi = wg2x2.shard.shard_range(total, world, rank)
+    n = hi - lo
+    model = ResNet18Var(stage5_pool=not args.stage5_at_14, math=args.math).to(dev).eval()
+    gen = torch.Generator().manual_seed(100 + rank)
+    imgs_h = torch.randn((n, 3, 224, 224), generator=gen).pin_memory()
+    imgs = [imgs_h.to(dev) + 0.0 * i for i in range(2)]
+    with torch.no_grad():
+        for i in range(args.warmup):
+            model(imgs[i % 2])
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        sampler = ClockSampler(local)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        wall0 = time.time()
+        a.record()
+        for i in range(args.steps):
+            model(imgs[i % 2])
+        b.record()
+        torch.cuda.synchronize()
+        clocks = sampler.finish(wall0, time.time())
+        t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.barrier()
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item()) / args.steps
+        # end to end: images from pinned host memory, logits back to the host
+        logits_h = torch.empty((n, 1000)).pin_memory()
+        xd = torch.empty_like(imgs[0])
+        e2e_steps = max(3, min(args.steps, 10))
+
+        def e2e():
+            xd.copy_(imgs_h, non_blocking=True)
+            logits_h.copy_(model(xd), non_blocking=True)
+
+        e2e()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a.record()
+        for _ in range(e2e_steps):
+            e2e()
+        b.record()
+        torch.cuda.synchronize()
+        te = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te.item()) / e2e_steps
+    if rank == 0:
+        flops = model.winograd_flops(total)
+        print(json.dumps({
+            "metric": "resnet18_var_forward_throughput", "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
+            "config": {"workload": "cfg4", "total_batch": total, "per_gpu_batch": n, "image": 224,
+                       "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": "NCHW",
+                       "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; stem, pools, 1x1 shortcuts, BN, FC on stock torch",
+                       "l2": "two rotating image batches; activations of a step exceed L2 many times over"},
+            "winograd_tflops_dense": flops / (ms * 1e-3) / 1e12, "clocks": clocks,
+            "e2e": {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": imgs_h.numel() * 4,
+                    "d2h_bytes_per_step": logits_h.numel() * 4, "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps * 32,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -154,19 +233,28 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default=os.environ.get("WG2X2_BENCH_MATH", "tf32"), choices=["tf32", "fp32"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
+    ap.add_argument("--stage5-at-14", action="store_true", help="cfg4: leave pool4 out, as the reference script does")
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
     ap.add_argument("--e2e-chunks", type=int, default=4, help="chunks of the host-buffer pipeline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    wl = dict(WORKLOADS[args.workload])
-    if args.batch > 0:
-        wl["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload == "cfg4":
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the network-level reference needs TensorFlow 1.3 + tensorpack, "
+                                  "absent here; the layer-level CPU restatement is timed by the cfg2 workload"}))
+            return
+        run_resnet(args, rank, world, local)
+        return
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["B"] = args.batch
 
     if args.impl == "reference":
         run_reference(args, wl, rank, world)

@@ -1,0 +1,135 @@
+"""ResNet-18-var forward graph around the Winograd-ReLU layers (inference form).
+
+Topology as in the reference's Model._build_graph
+(ResNet-18-var/imagenet-resnet-transWino-prune.py:113-220): 7x7/2 stem, 3x3/2 SAME max-pools, four
+stages of two blocks; every 3x3 convolution is BatchNorm -> WinogradImTrans(relu) -> WinogradConv;
+the `a` blocks carry a 1x1 shortcut convolution + BatchNorm, the `b` blocks an identity shortcut
+after a ReLU.  The reference has `pool4` commented out (:191), so its stage 5 runs at 14x14;
+`stage5_pool=True` restores the pool (7x7), which is the shape the benchmark configuration names.
+
+Only the Winograd layers run on this repository's kernels (NCHW); the stem, pools, 1x1 shortcuts,
+BatchNorm affine maps and the classifier are stock torch ops.  Weights are random (seeded): there is
+no checkpoint to load here.
+"""
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+import wg2x2
+
+STAGES = ((64, 64), (64, 128), (128, 256), (256, 512))       # (channels in, channels out) per stage
+DENSITY = (0.6, 0.4, 0.3, 0.2)                               # Winograd-domain weight density per stage
+
+
+def _same_pool(x):
+    """MaxPooling(3, stride=2, padding='SAME') of TensorFlow: for even sizes the one pad row/column goes
+    at the bottom/right."""
+    H, W = x.shape[2], x.shape[3]
+    ph = max((-(-H // 2) - 1) * 2 + 3 - H, 0)
+    pw = max((-(-W // 2) - 1) * 2 + 3 - W, 0)
+    x = F.pad(x, (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2), value=float("-inf"))
+    return F.max_pool2d(x, 3, 2)
+
+
+class _BN(torch.nn.Module):
+    """Inference BatchNorm as a per-channel affine map (scale, shift)."""
+
+    def __init__(self, ch, gen):
+        super().__init__()
+        self.register_buffer("scale", 1.0 + 0.1 * torch.randn(ch, generator=gen))
+        self.register_buffer("shift", 0.1 * torch.randn(ch, generator=gen))
+
+    def forward(self, x):
+        return x * self.scale.view(1, -1, 1, 1) + self.shift.view(1, -1, 1, 1)
+
+
+class _WinogradLayer(torch.nn.Module):
+    """WinogradImTrans(relu) + WinogradConv with a fixed pruning mask."""
+
+    def __init__(self, cin, cout, density, gen):
+        super().__init__()
+        std = (1.3 * (2.0 * 9.0 / 32.0) / (16 * cin)) ** 0.5       # the reference's default initialiser scale
+        w = std * torch.randn((16, cin, cout), generator=gen)
+        mask = (torch.rand((16, cin, cout), generator=gen) < density).float()
+        self.register_buffer("W", (w * mask).contiguous())
+        self.register_buffer("mask", mask)
+        self.cout = cout
+        self._prepared = None
+
+    def forward(self, x, math="tf32"):
+        B, C, H, W = x.shape
+        v = wg2x2.imtrans_fwd(x.contiguous(), relu=True, layout="NCHW")
+        if math == "tf32":
+            if self._prepared is None or self._prepared.device != x.device:
+                self._prepared = wg2x2.prepare_weights(self.W)
+            return wg2x2.conv_fwd_prepared(v, self._prepared, self.cout, H, W, layout="NCHW")
+        return wg2x2.conv_fwd(v, self.W, H, W, layout="NCHW", math="fp32")
+
+    def forward_reference(self, x):
+        """The same layer from the transform matrices with float64 einsums (for tests)."""
+        BT = torch.tensor([[1, 0, -1, 0], [0, 1, 1, 0], [0, -1, 1, 0], [0, 1, 0, -1]], dtype=torch.float64, device=x.device)
+        AT = torch.tensor([[1, 1, 1, 0], [0, 1, -1, -1]], dtype=torch.float64, device=x.device)
+        B, C, H, W = x.shape
+        nH, nW = (H + 1) // 2, (W + 1) // 2
+        xp = F.pad(x.double(), (1, 2 * nW + 1 - W, 1, 2 * nH + 1 - H))
+        d = torch.stack([torch.stack([xp[:, :, y:y + 2 * nH:2, s:s + 2 * nW:2] for s in range(4)], -1) for y in range(4)], -2)
+        v = torch.relu(torch.einsum("iy,bchwyx,jx->ijbhwc", BT, d, BT))
+        m = torch.einsum("ijbhwc,ijck->ijbhwk", v, self.W.double().view(4, 4, C, self.cout))
+        y = torch.einsum("ai,ijbhwk,ej->bkhawe", AT, m, AT).reshape(B, self.cout, 2 * nH, 2 * nW)
+        return y[:, :, :H, :W].float()
+
+
+class ResNet18Var(torch.nn.Module):
+    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32"):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        self.math = math
+        self.stage5_pool = stage5_pool
+        self.stem = torch.nn.Parameter(torch.randn((64, 3, 7, 7), generator=gen) * (2.0 / (49 * 64)) ** 0.5, requires_grad=False)
+        self.blocks = torch.nn.ModuleList()
+        for s, (cin, cout) in enumerate(STAGES):
+            blk_a = torch.nn.ModuleDict(dict(
+                bn2a=_BN(cin, gen), w2a=_WinogradLayer(cin, cout, DENSITY[s], gen), bn2b=_BN(cout, gen),
+                w2b=_WinogradLayer(cout, cout, DENSITY[s], gen), bn2c=_BN(cout, gen), bn1=_BN(cout, gen)))
+            blk_a.short = torch.nn.Parameter(torch.randn((cout, cin, 1, 1), generator=gen) * (2.0 / cout) ** 0.5, requires_grad=False)
+            if s == 0:
+                blk_a["pre"] = _BN(cin, gen)          # res2a_1_relu is BNReLU in the reference, plain ReLU in later stages
+            blk_b = torch.nn.ModuleDict(dict(
+                bn2a=_BN(cout, gen), w2a=_WinogradLayer(cout, cout, DENSITY[s], gen), bn2b=_BN(cout, gen),
+                w2b=_WinogradLayer(cout, cout, DENSITY[s], gen), bn2c=_BN(cout, gen)))
+            self.blocks.append(torch.nn.ModuleList([blk_a, blk_b]))
+        self.fc_w = torch.nn.Parameter(torch.randn((num_classes, 512), generator=gen) * (1.0 / 512) ** 0.5, requires_grad=False)
+        self.fc_b = torch.nn.Parameter(torch.zeros(num_classes), requires_grad=False)
+
+    def _branch(self, blk, l, ref):
+        conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math))
+        t = conv(blk["w2a"], blk["bn2a"](l))
+        t = conv(blk["w2b"], blk["bn2b"](t))
+        return blk["bn2c"](t)
+
+    def forward(self, image, reference=False):
+        """image: (B,3,H,W) float32, already normalised.  reference=True computes the Winograd layers with
+        float64 einsums instead of this repository's kernels."""
+        l = F.conv2d(F.pad(image, (2, 3, 2, 3)), self.stem, stride=2)   # 7x7/2 with TensorFlow's SAME padding
+        l = _same_pool(l)
+        for s, (blk_a, blk_b) in enumerate(self.blocks):
+            bra = self._branch(blk_a, l, reference)
+            main = torch.relu(blk_a["pre"](l)) if s == 0 else torch.relu(l)
+            l = blk_a["bn1"](F.conv2d(main, blk_a.short)) + bra
+            bra = self._branch(blk_b, l, reference)
+            l = torch.relu(l) + bra
+            if s < 2 or (s == 2 and self.stage5_pool):
+                l = _same_pool(l)
+        l = torch.relu(l).mean(dim=(2, 3))
+        return F.linear(l, self.fc_w, self.fc_b)
+
+    def winograd_flops(self, batch, size=224):
+        """Dense Winograd-domain flops 2*16*P*C*K summed over the 16 layers (independent of the masks)."""
+        sp = size // 4
+        total = 0
+        for s, (cin, cout) in enumerate(STAGES):
+            P = batch * ((sp + 1) // 2) ** 2
+            total += 2 * 16 * P * (cin * cout + 3 * cout * cout)
+            if s < 2 or (s == 2 and self.stage5_pool):
+                sp = (sp + 1) // 2
+        return total

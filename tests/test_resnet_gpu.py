@@ -1,0 +1,28 @@
+"""ResNet-18-var forward graph: the Winograd layers on this library's kernels against the same graph with
+the layers computed from the transform matrices in float64 (torch einsum)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("math,tol", [("fp32", 2e-4), ("tf32", 2e-2)])
+@pytest.mark.parametrize("stage5_pool", [True, False])
+def test_forward_matches_einsum_graph(math, tol, stage5_pool):
+    from resnet18_var import ResNet18Var
+    torch.manual_seed(0)
+    model = ResNet18Var(stage5_pool=stage5_pool, seed=3, math=math).cuda().eval()
+    x = torch.randn((2, 3, 96, 96), device="cuda")       # 24x24 at stage 2 ... 3x3 (odd) at stage 5
+    with torch.no_grad():
+        got = model(x)
+        want = model(x, reference=True)
+    assert got.shape == (2, 1000) and torch.isfinite(got).all()
+    err = float((got - want).abs().max() / want.abs().max())
+    assert err <= tol, err   # 16 layers deep: per-layer 1e-5 / 5e-3 compounds
+
+
+def test_winograd_flops_count():
+    from resnet18_var import ResNet18Var
+    m = ResNet18Var(stage5_pool=True)
+    assert abs(m.winograd_flops(1) / 1e6 - 1600.2) < 1.0      # MFLOP per image, stage 5 at 7x7
+    assert abs(ResNet18Var(stage5_pool=False).winograd_flops(1) / 1e6 - 2569.0) < 1.5   # at 14x14, as the reference runs it
