@@ -147,6 +147,73 @@ def run_reference(args, wl, rank, world):
     }))
 
 
+def run_backward(args, rank, world, local):
+    """BASELINE config 5: backward of a pruned conv5_x-shaped layer (N=256, C=K=512, 7x7, density 0.2):
+    dX through the transposed products plus the input-transform gradient (ReLU mask applied), and the
+    masked dW.  Per-GPU batch fixed (weak scaling); dW would need one all-reduce when sharded, which is
+    reported separately and not part of the step."""
+    import torch
+    import torch.distributed as dist
+    import wg2x2
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, C, K, H, W = (args.batch if args.batch > 0 else 256), 512, 512, 7, 7
+    nH = nW = 4
+    P = B * nH * nW
+    g = torch.Generator().manual_seed(1 + rank)
+    X = torch.randn((B, C, H, W), generator=g).to(dev)
+    mask = (torch.rand((16, C, K), generator=torch.Generator().manual_seed(3)) < 0.2).float().to(dev)
+    Wt = (0.05 * torch.randn((16, C, K), generator=torch.Generator().manual_seed(2))).to(dev) * mask
+    dYs = [torch.randn((B, K, H, W), generator=g).to(dev) for _ in range(2)]
+    V = wg2x2.imtrans_fwd(X, relu=True, layout="NCHW")
+
+    def step(i):
+        dV, dW = wg2x2.conv_bwd(V, Wt, dYs[i % 2], mask=mask, layout="NCHW", relu=True, math=args.bwd_math)
+        dX = wg2x2.imtrans_bwd(dV, H, W, layout="NCHW")
+        return dX, dW
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
+    a.record()
+    for i in range(args.steps):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    clocks = sampler.finish(wall0, time.time())
+    t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    if rank == 0:
+        pk = peaks()
+        flops = 2.0 * 2 * 16 * P * C * K
+        bytes_alg = 4.0 * B * K * H * W + 64.0 * P * C + 2 * 64.0 * C * K + 4.0 * B * C * H * W + 64.0 * C * K
+        print(json.dumps({
+            "metric": "winograd_relu_conv_layer_bwd_throughput", "value": world * B / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "tf32" if args.bwd_math == "tf32" else "f32", "data": "synthetic",
+            "config": {"workload": "cfg5", "layer": dict(B=B, C=C, K=K, H=H, W=W, density=0.2), "layout": "NCHW",
+                       "l2": "two rotating dY buffers; V (%.0f MB) and dV exceed L2" % (64.0 * P * C / 1e6)},
+            "layer_tflops": flops * world / (ms * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["bf16_tflops"] / 2, "unit": "TFLOP/s",
+                         "frac": flops / (ms * 1e-3) / 1e12 / (pk["bf16_tflops"] / 2), "traffic": None,
+                         "algorithmic_bytes": bytes_alg, "peak_source": pk["source"] + " bf16 / 2"},
+            "clocks": clocks, "gpu_launches": args.steps * 4,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_resnet(args, rank, world, local):
     """BASELINE config 4: ResNet-18-var forward, batch 256 in total, sharded over the ranks (strong scaling)."""
     import torch
@@ -233,7 +300,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default=os.environ.get("WG2X2_BENCH_MATH", "tf32"), choices=["tf32", "fp32"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "cfg5"])
+    ap.add_argument("--bwd-math", default="fp32", choices=["fp32", "tf32"], help="cfg5: math mode of the gradient products")
     ap.add_argument("--stage5-at-14", action="store_true", help="cfg4: leave pool4 out, as the reference script does")
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
@@ -251,6 +319,14 @@ def main():
                                   "absent here; the layer-level CPU restatement is timed by the cfg2 workload"}))
             return
         run_resnet(args, rank, world, local)
+        return
+    if args.workload == "cfg5":
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "backward CPU timing is not part of the reference arm; "
+                                  "the forward layer (cfg2 workload) is"}))
+            return
+        run_backward(args, rank, world, local)
         return
     wl = dict(WORKLOADS[args.workload])
     if args.batch > 0:

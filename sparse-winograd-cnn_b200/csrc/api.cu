@@ -24,6 +24,9 @@ size_t prepared_weights_bytes(int C, int K);
 int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
                          int layout, cudaStream_t st);
+size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW);
+int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *mask, float *dV, float *dW, int B, int H, int W,
+                int C, int K, int layout, int relu, void *ws, size_t ws_bytes, cudaStream_t st);
 }  // namespace wg
 
 using namespace wg;
@@ -96,9 +99,10 @@ int wg2x2_conv_fwd_prepared(const float *V, const void *prepared, float *Y, int 
 
 size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int want_dW)
 {
-    (void)math;
-    if (!want_dW || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return 0;
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return 0;
     const long long P = (long long)B * ((H + 1) / 2) * ((W + 1) / 2);
+    if (math == WG2X2_MATH_TF32) return conv_bwd_tc_workspace_bytes(P, C, K, want_dW);
+    if (!want_dW) return 0;
     return conv_dw_scratch_bytes(P, C, K);
 }
 
@@ -109,8 +113,9 @@ int wg2x2_conv_bwd(const float *V, const float *Wt, const float *dY, const float
     if (!layout_ok(layout) || !math_ok(math)) return WG2X2_ERR_BAD_ARG;
     if (dV && !Wt) return WG2X2_ERR_BAD_ARG;
     if ((dW || (dV && relu)) && !V) return WG2X2_ERR_BAD_ARG;
-    if (math != WG2X2_MATH_FP32) return WG2X2_ERR_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
+    if (math == WG2X2_MATH_TF32)
+        return conv_bwd_tc(V, Wt, dY, mask, dV, dW, B, H, W, C, K, layout, relu, workspace, workspace_bytes, st);
     if (dV) {
         const int s = conv_dv_ffma(V, Wt, dY, dV, B, H, W, C, K, layout, relu, st);
         if (s != WG2X2_OK) return s;

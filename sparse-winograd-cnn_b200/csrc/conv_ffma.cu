@@ -358,6 +358,12 @@ __global__ void __launch_bounds__(256) conv_dw_reduce_kernel(const float *__rest
     }
 }
 
+void dw_reduce_launch(const float *partial, const float *mask, float *dW, long long n, int splits, cudaStream_t st)
+{
+    const int blocks = (int)min((long long)kNumSMs * 8, cdivll(n, 256));
+    conv_dw_reduce_kernel<<<blocks, 256, 0, st>>>(partial, mask, dW, n, splits);
+}
+
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------

@@ -27,7 +27,7 @@ class _Conv(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         I, W = ctx.saved_tensors
-        dV, dW = _ops.conv_bwd(I, W, grad.contiguous(), layout=ctx.data_format, math="fp32",
+        dV, dW = _ops.conv_bwd(I, W, grad.contiguous(), layout=ctx.data_format, math=ctx.math,
                                need_dV=ctx.needs_input_grad[0], need_dW=ctx.needs_input_grad[1])
         return dV, dW, None, None, None
 
@@ -36,5 +36,5 @@ def winograd2x2_conv(I, W, out_hw=None, data_format="NHWC", math="fp32"):
     return _Conv.apply(I, W, out_hw, data_format, math)
 
 
-def winograd2x2_conv_grad(i1, i2, grad, data_format="NHWC"):
-    return _ops.conv_bwd(i1.contiguous(), i2.contiguous(), grad.contiguous(), layout=data_format)
+def winograd2x2_conv_grad(i1, i2, grad, data_format="NHWC", math="fp32"):
+    return _ops.conv_bwd(i1.contiguous(), i2.contiguous(), grad.contiguous(), layout=data_format, math=math)

@@ -117,3 +117,38 @@ def test_unsupported_shape_reports(wg):
     with pytest.raises(wg.Wg2x2Error) as e:
         wg.conv_fwd(V, Wt, math="tf32")
     assert e.value.status == -5
+
+
+BWD_SHAPES = [  # B, H, W, C, K
+    (2, 14, 14, 64, 64), (3, 6, 6, 32, 64), (2, 7, 7, 64, 128), (1, 28, 28, 128, 96), (2, 9, 13, 36, 20),
+    (3, 14, 14, 256, 256), (4, 56, 56, 64, 64), (16, 7, 7, 512, 512), (2, 8, 8, 320, 288),
+]
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("shape", BWD_SHAPES)
+def test_conv_bwd_tf32(wg, oracle, shape, layout):
+    """dV (with the ReLU mask) and masked dW from the tensor-core gradient kernels."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    rng = np.random.default_rng(1 + sum(shape))
+    dY = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    mask = (rng.random((16, C, K)) < 0.3).astype(np.float32)
+    Wm = Wt * mask
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    dVo, dWo = oracle.conv_bwd(V, Wm, dY, mask=mask)
+    dyl = dY if layout == "NHWC" else np.ascontiguousarray(np.transpose(dY, (0, 3, 1, 2)))
+    dV, dW = wg.conv_bwd(_dev(V), _dev(Wm), _dev(dyl), mask=_dev(mask), layout=layout, relu=True, math="tf32")
+    _status_ok(wg)
+    dV, dW = dV.cpu().numpy(), dW.cpu().numpy()
+    assert np.isfinite(dV).all() and np.isfinite(dW).all()
+    e_dv = oracle.max_rel(dV, dVo * (V > 0))
+    e_dw = oracle.max_rel(dW, dWo)
+    assert e_dv <= TOL_TF32 and e_dw <= TOL_TF32, "dV %.3g dW %.3g" % (e_dv, e_dw)
+    assert (dV[V <= 0] == 0).all() and (dW[mask == 0] == 0).all()
+    # dV alone, without the mask, and dW alone
+    dV2, none = wg.conv_bwd(_dev(V), _dev(Wm), _dev(dyl), layout=layout, math="tf32", need_dW=False)
+    assert none is None and oracle.max_rel(dV2.cpu().numpy(), dVo) <= TOL_TF32
+    none, dW2 = wg.conv_bwd(_dev(V), _dev(Wm), _dev(dyl), layout=layout, math="tf32", need_dV=False)
+    assert none is None and oracle.max_rel(dW2.cpu().numpy(), oracle.conv_bwd(V, Wm, dY)[1]) <= TOL_TF32
+    _status_ok(wg)
