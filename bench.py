@@ -171,8 +171,8 @@ def run_backward(args, rank, world, local):
     V = wg2x2.imtrans_fwd(X, relu=True, layout="NCHW")
 
     def step(i):
-        dV, dW = wg2x2.conv_bwd(V, Wt, dYs[i % 2], mask=mask, layout="NCHW", relu=True, math=args.bwd_math)
-        dX = wg2x2.imtrans_bwd(dV, H, W, layout="NCHW")
+        dV, dW = wg2x2.conv_bwd(V, Wt, dYs[i % 2], mask=mask, layout="NCHW", relu=False, math=args.bwd_math)
+        dX = wg2x2.imtrans_bwd(dV, H, W, V_relu=V, layout="NCHW")   # ReLU mask applied inside the gather
         return dX, dW
 
     for i in range(args.warmup):

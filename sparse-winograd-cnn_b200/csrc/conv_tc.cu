@@ -14,7 +14,6 @@
 // and returns (status readable through wg2x2_last_device_status).
 #include <cuda.h>
 
-#pragma nv_diag_suppress 128   // "loop is not reachable": mode-specific code after a compile-time branch
 
 #include "wg_common.cuh"
 
@@ -204,8 +203,7 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restri
 // Main kernel
 // ---------------------------------------------------------------------------------------
 struct TcParams {
-    float *Y;                 // forward: the image-like output; plane mode: 16 planes [t][P][K]
-    const float *plane_mask;  // plane mode: where this tensor (same shape as Y) is <= 0 the output is zeroed; may be null
+    float *Y;
     const unsigned long long *masks;
     long long P;
     int nH, nW, C, K, outH, outW;
@@ -214,9 +212,7 @@ struct TcParams {
     int units;
 };
 
-// MODE 0: forward (row walk + A^T m A, image-like output in LAYOUT).
-// MODE 1: plain products, every accumulator is an output plane Y[t][p][0..K) (used for dV = dM . W^T).
-template <int LAYOUT, int MODE>
+template <int LAYOUT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams prm)
 {
@@ -336,68 +332,6 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         int tr = 0; (void)tr;
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
             const int mt = u / prm.nKB, kb = u % prm.nKB;
-            if (MODE == 1) {
-                // ---- plane mode: no output transform, 16 output planes ----
-                const long long p = (long long)mt * prm.tpu + q * 32 + lane;
-                const bool tile_ok = (q * 32 + lane < prm.tpu) && p < prm.P;
-                const int cbase = kb * kBlockN + half * 32;
-                const bool vec = (cbase + 32 <= prm.K) && ((prm.K & 3) == 0);
-                float *stg = epi_stage_all + ew * (kEpiStageBytes / 4);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int buf = i & 1;
-                    if (ok && !mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
-                    acc_use[buf]++;
-                    if (!ok) continue;
-                    tc_fence_after();
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 4 * kBlockN + half * 32);
-                    float r[4][32];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) tmem_ld8(taddr + (uint32_t)(j * kBlockN + ch * 8), &r[j][ch * 8]);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acce_bar(buf));   // TMEM buffer free again; stores follow from registers
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const long long my_off = tile_ok ? ((long long)(4 * i + j) * prm.P + p) * prm.K + cbase : -1;
-                        if (vec) {
-                            __syncwarp();
-#pragma unroll
-                            for (int c8 = 0; c8 < 8; ++c8)
-                                *reinterpret_cast<float4 *>(stg + lane * 32 + ((c8 ^ (lane & 7)) << 2)) =
-                                    make_float4(r[j][4 * c8], r[j][4 * c8 + 1], r[j][4 * c8 + 2], r[j][4 * c8 + 3]);
-                            __syncwarp();
-#pragma unroll
-                            for (int rr = 0; rr < 8; ++rr) {
-                                const int row = 4 * rr + (lane >> 3), ch = lane & 7;
-                                const long long off = __shfl_sync(0xffffffffu, my_off, row);
-                                float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
-                                if (off >= 0) {
-                                    if (prm.plane_mask) {
-                                        const float4 mk = __ldg(reinterpret_cast<const float4 *>(prm.plane_mask + off + 4 * ch));
-                                        v.x = mk.x > 0.f ? v.x : 0.f; v.y = mk.y > 0.f ? v.y : 0.f;
-                                        v.z = mk.z > 0.f ? v.z : 0.f; v.w = mk.w > 0.f ? v.w : 0.f;
-                                    }
-                                    *reinterpret_cast<float4 *>(prm.Y + off + 4 * ch) = v;
-                                }
-                            }
-                        } else if (tile_ok) {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c) {
-                                if (cbase + c >= prm.K) continue;
-                                float v = r[j][c];
-                                if (prm.plane_mask && !(__ldg(prm.plane_mask + my_off + c) > 0.f)) v = 0.f;
-                                prm.Y[my_off + c] = v;
-                            }
-                        }
-                    }
-                }
-                if (!ok) break;
-                continue;
-            }
             float y[4][32];                // [2a+e][column]
 #pragma unroll
             for (int o = 0; o < 4; ++o)
@@ -578,16 +512,14 @@ int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes,
     return launch_status();
 }
 
-// Common launcher.  `contr` = contraction length (C forward, K for dV), `ncols` = output columns
-// (K forward, C for dV); A is (16, P, contr), Bop is (16, ncols, contr), both contraction-contiguous.
-static int tc_launch(int mode, int layout, const float *A, const float *Bop, const unsigned long long *masks, float *out,
-                     const float *plane_mask, long long P, int nH, int nW, int contr, int ncols, int outH, int outW,
-                     cudaStream_t st)
+// Launcher.  `contr` = contraction length C, `ncols` = output channels K; A is (16, P, contr), Bop is
+// (16, ncols, contr), both contraction-contiguous.
+static int tc_launch(int layout, const float *A, const float *Bop, const unsigned long long *masks, float *out, long long P,
+                     int nH, int nW, int contr, int ncols, int outH, int outW, cudaStream_t st)
 {
     if (P > 0x7fffffffLL - kBlockM) return WG2X2_ERR_UNSUPPORTED;
     TcParams prm;
     prm.Y = out;
-    prm.plane_mask = plane_mask;
     prm.masks = masks;
     prm.P = P; prm.nH = nH; prm.nW = nW; prm.C = contr; prm.K = ncols; prm.outH = outH; prm.outW = outW;
     prm.nKB = cdiv(ncols, kBlockN);
@@ -612,16 +544,15 @@ static int tc_launch(int mode, int layout, const float *A, const float *Bop, con
     if (!make_map(&mapA, A, contr, P, kBlockM)) return WG2X2_ERR_LAUNCH;
     if (!make_map(&mapB, Bop, contr, ncols, kBlockN)) return WG2X2_ERR_LAUNCH;
     const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
-#define WG_TC_LAUNCH(L, M)                                                                                              \
+#define WG_TC_LAUNCH(L)                                                                                                 \
     do {                                                                                                                \
-        if (cudaFuncSetAttribute(conv_fwd_tc_kernel<L, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=  \
+        if (cudaFuncSetAttribute(conv_fwd_tc_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=     \
             cudaSuccess)                                                                                                \
             return WG2X2_ERR_LAUNCH;                                                                                    \
-        conv_fwd_tc_kernel<L, M><<<grid, kTcThreads, kSmemBytes, st>>>(mapA, mapB, prm);                                \
+        conv_fwd_tc_kernel<L><<<grid, kTcThreads, kSmemBytes, st>>>(mapA, mapB, prm);                                   \
     } while (0)
-    if (mode == 1) WG_TC_LAUNCH(WG2X2_NHWC, 1);
-    else if (layout == WG2X2_NHWC) WG_TC_LAUNCH(WG2X2_NHWC, 0);
-    else WG_TC_LAUNCH(WG2X2_NCHW, 0);
+    if (layout == WG2X2_NHWC) WG_TC_LAUNCH(WG2X2_NHWC);
+    else WG_TC_LAUNCH(WG2X2_NCHW);
 #undef WG_TC_LAUNCH
     return launch_status();
 }
@@ -634,8 +565,7 @@ int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, 
     if ((reinterpret_cast<uintptr_t>(V) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 15u)) return WG2X2_ERR_BAD_ARG;
     const unsigned long long *masks = reinterpret_cast<const unsigned long long *>(
         static_cast<const unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256));
-    return tc_launch(0, layout, V, static_cast<const float *>(prepared), masks, Y, nullptr, (long long)B * nH * nW, nH, nW, C, K,
-                     outH, outW, st);
+    return tc_launch(layout, V, static_cast<const float *>(prepared), masks, Y, (long long)B * nH * nW, nH, nW, C, K, outH, outW, st);
 }
 
 size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K)

@@ -2,9 +2,9 @@
 // PTX wrappers, the status word and the plane-mode instantiation of the tcgen05 kernel).
 //
 //   dM  = A dY A^T           conv_dm_*_kernel: one HBM-bound pass, 16 planes [t][P][K], rounded to TF32
-//   dV_t = dM_t . W_t^T      the forward tcgen05 kernel in plane mode (A = dM, B = W as stored: (16,C,K)
-//                            is already contraction-contiguous for this product), ReLU mask in the epilogue
-//   dW_t = V_t^T . dM_t      conv_dw_tc_kernel below (both operands MN-major), split over P
+//   dV_t = dM_t . W_t^T      conv_grad_gemm_tc_kernel<1> (A = dM, B = W as stored: (16,C,K) is already
+//                            contraction-contiguous for this product), ReLU mask in the epilogue
+//   dW_t = V_t^T . dM_t      conv_grad_gemm_tc_kernel<0> (both operands MN-major), split over P
 #pragma once
 
 // ---------------------------------------------------------------------------------------
@@ -120,10 +120,10 @@ static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int
 }
 
 // ---------------------------------------------------------------------------------------
-// Workspace of the tensor-core backward pass: [dM | W rounded to TF32 | all-ones block masks | dW partials]
+// Workspace of the tensor-core backward pass: [dM | W rounded to TF32 | dW partials]
 // ---------------------------------------------------------------------------------------
 struct BwdWs {
-    size_t dm, wr, masks, partial, total;
+    size_t dm, wr, partial, total;
 };
 static BwdWs bwd_ws_layout(long long P, int C, int K, int dw_splits)
 {
@@ -131,7 +131,6 @@ static BwdWs bwd_ws_layout(long long P, int C, int K, int dw_splits)
     w.dm = 0;
     size_t off = align_up((size_t)16 * P * K * sizeof(float), 256);
     w.wr = off;      off += align_up((size_t)16 * C * K * sizeof(float), 256);
-    w.masks = off;   off += align_up((size_t)16 * cdiv(C, kBlockN) * sizeof(unsigned long long), 256);
     w.partial = off; off += dw_splits > 1 ? align_up((size_t)dw_splits * 16 * C * K * sizeof(float), 256) : 0;
     w.total = off;
     return w;
@@ -139,43 +138,42 @@ static BwdWs bwd_ws_layout(long long P, int C, int K, int dw_splits)
 
 bool tc_bwd_shape_supported(int C, int K) { return C % 4 == 0 && K % 4 == 0 && C >= 4 && K >= 4; }
 
-int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, unsigned long long *masks, float *dV, long long P,
-               int C, int K, int relu, cudaStream_t st)
-{
-    const long long n = (long long)16 * C * K;
-    round_tf32_kernel<<<(int)min((long long)kNumSMs * 8, cdivll(n, 256)), 256, 0, st>>>(Wt, Wr, n);
-    if (launch_status() != WG2X2_OK) return WG2X2_ERR_LAUNCH;
-    if (cudaMemsetAsync(masks, 0xFF, (size_t)16 * cdiv(C, kBlockN) * sizeof(unsigned long long), st) != cudaSuccess)
-        return WG2X2_ERR_LAUNCH;
-    // A = dM (16, P, K), B = W (16, C, K): contraction over K, C output columns
-    return tc_launch(1, WG2X2_NHWC, dM, Wr, masks, dV, relu ? V : nullptr, P, 1, 1, K, C, 0, 0, st);
-}
-
 // ---------------------------------------------------------------------------------------
-// dW_t[c][k] = sum_p V_t[p][c] dM_t[p][k] on the tensor cores.
+// The two gradient products as plain batched GEMMs on the tensor cores (16 independent positions):
 //
-// Both operands are stored with the contraction index p as the slow axis, i.e. they are "MN-major" for
-// UMMA: a [32 p x 32 channel] box lands in shared memory as 32 rows of 128 bytes (128B swizzle, 32B atoms),
-// which is one MN block of 32 channels x eight K groups of 4 tiles.  A (V_t^T, M = 128 input channels) is four such
-// boxes 4 KB apart (the descriptor's leading-dimension offset), B (dM_t, N = 64/128/256 output channels) is
-// N/32 of them.  One MMA (K = 8 tiles) reads 8 rows: start address + 1024 B per step.
-// Unit = (position t, 128-channel block of C, N-channel block of K, split of the P range); accumulator in
-// TMEM (N columns, double-buffered); the epilogue writes the [128 x N] tile -- dW itself (times the mask)
-// when there is one split, else that split's partial sum for conv_dw_reduce_kernel.
+//   KIND 0   dW_t[c][k] = sum_p V_t[p][c] dM_t[p][k]    rows = C, columns = K, contraction over P (split)
+//   KIND 1   dV_t[p][c] = sum_k dM_t[p][k] W_t[c][k]    rows = P, columns = C, contraction over K
+//
+// Unit = (position t, block of 128 rows, block of N = 64/128/256 columns[, split of the contraction]);
+// one fp32 accumulator of N TMEM columns, double-buffered, so the epilogue of a unit overlaps the MMAs of
+// the next.  A wide N is what makes these run well: the A tile is read from shared memory and from L2 once
+// per 128 x N x 32 products.
+//
+// KIND 0 operands are stored with the contraction index p as the slow axis, i.e. "MN-major" for UMMA: a
+// [32 p x 32 channel] box lands in shared memory as 32 rows of 128 bytes (128B swizzle, 32B atoms), which
+// is one MN block of 32 channels x eight K groups of 4 tiles.  A (V_t^T, 128 input channels) is four such
+// boxes 4 KB apart (the descriptor's leading-dimension offset), B (dM_t) is N/32 of them.  One MMA (K = 8)
+// reads 8 rows: start address + 1024 B per step.
+// KIND 1 operands are contraction-contiguous ("K-major"): A = a [128 p x 32 k] box of dM, B = an [N x 32 k]
+// box of W exactly as the reference stores it, both with the plain 128B swizzle; + 32 B per MMA step.
+//
+// The epilogue turns each 32 x 32 block through shared memory so that stores are whole 128-byte lines, and
+// applies the pruning mask (KIND 0, one split) or the ReLU mask V > 0 (KIND 1) on the way out.
 // ---------------------------------------------------------------------------------------
-constexpr int kDwStages = 4;
-constexpr int kDwBoxBytes = 32 * 32 * 4;                 // [32 p][32 ch] fp32
-constexpr int kDwABytes = 4 * kDwBoxBytes;               // 128 input channels
-constexpr int kDwBBytesMax = 8 * kDwBoxBytes;            // up to 256 output channels
-constexpr int kDwStageBytes = kDwABytes + kDwBBytesMax;  // 48 KB
-constexpr int kDwSmemBytes = kDwStages * kDwStageBytes + 1024 + kCtrlBytes + kEpiWarps * kEpiStageBytes;
+constexpr int kGgStages = 4;
+constexpr int kGgBoxBytes = 32 * 32 * 4;                 // [32 rows][32 fp32]
+constexpr int kGgABytes = 4 * kGgBoxBytes;               // 128 rows x 32 contraction steps
+constexpr int kGgBBytesMax = 8 * kGgBoxBytes;            // up to 256 columns
+constexpr int kGgStageBytes = kGgABytes + kGgBBytesMax;  // 48 KB
+constexpr int kGgSmemBytes = kGgStages * kGgStageBytes + 1024 + kCtrlBytes + kEpiWarps * kEpiStageBytes;
 
-struct DwParams {
-    float *out;
-    const float *mask;
-    long long P;
-    int C, K, N;
-    int nCB, nKB;
+struct GgParams {
+    float *out;              // [split][16][rows][cols] (split dimension only when !direct)
+    const float *mask;       // KIND 0: multiplies the result (direct only); KIND 1: result zeroed where mask <= 0
+    long long rows;          // C (KIND 0) or P (KIND 1)
+    long long contr;         // P (KIND 0) or K (KIND 1)
+    int cols, N;
+    int nRB, nCB;
     int splits, chunks_per_split;
     int units;
     int direct;
@@ -189,33 +187,34 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr)
 {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)(kDwBoxBytes >> 4) << 16;
+    d |= (uint64_t)(kGgBoxBytes >> 4) << 16;
     d |= (uint64_t)(512 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)1 << 61;
     return d;
 }
 
+template <int KIND>
 __global__ void __launch_bounds__(kTcThreads, 1)
-conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapM, const DwParams prm)
+conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GgParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen_base = smem_raw + (base - raw);
-    const uint32_t bars = base + kDwStages * kDwStageBytes;
-    uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kDwStages * kDwStageBytes);
+    const uint32_t bars = base + kGgStages * kGgStageBytes;
+    uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kGgStages * kGgStageBytes);
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (kDwStages + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * kDwStages + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * kDwStages + 2 + b); };
-    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + 2 * kDwStages + 4);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kDwStages + 5);
-    float *epi_stage_all = reinterpret_cast<float *>(gen_base + kDwStages * kDwStageBytes + kCtrlBytes);
+    auto empty_bar = [&](int s) { return bars + 8u * (kGgStages + s); };
+    auto accf_bar = [&](int b) { return bars + 8u * (2 * kGgStages + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (2 * kGgStages + 2 + b); };
+    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + 2 * kGgStages + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kGgStages + 5);
+    float *epi_stage_all = reinterpret_cast<float *>(gen_base + kGgStages * kGgStageBytes + kCtrlBytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kDwStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < kGgStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -230,37 +229,40 @@ conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constan
     const uint32_t tmem_base = *tmem_ptr_slot;
 
     const int N = prm.N;
-    const int per_t = prm.nCB * prm.nKB;
-    // unit -> (split, t, cb, kb), kb fastest so that neighbouring CTAs share the V tile in L2
-    auto decode = [&](int u, int &split, int &t, int &cb, int &kb) {
-        kb = u % prm.nKB; u /= prm.nKB;
+    // unit -> (split, t, row block, column block); column block fastest so that neighbouring CTAs share the A tile in L2
+    auto decode = [&](int u, int &split, int &t, int &rb, int &cb) {
         cb = u % prm.nCB; u /= prm.nCB;
+        rb = u % prm.nRB; u /= prm.nRB;
         t = u % 16;
         split = u / 16;
     };
-    (void)per_t;
 
     if (warp == 0) {
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool ok = true;
-            const uint32_t stage_tx = (uint32_t)(kDwABytes + (N / 32) * kDwBoxBytes);
+            const uint32_t stage_tx = (uint32_t)(kGgABytes + N * 128);
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
-                int split, t, cb, kb;
-                decode(u, split, t, cb, kb);
-                const long long pbeg = (long long)split * prm.chunks_per_split * 32;
-                const long long pend = min(prm.P, pbeg + (long long)prm.chunks_per_split * 32);
-                for (long long pc = pbeg; pc < pend; pc += 32) {
+                int split, t, rb, cb;
+                decode(u, split, t, rb, cb);
+                const long long kbeg = (long long)split * prm.chunks_per_split * 32;
+                const long long kend = min(prm.contr, kbeg + (long long)prm.chunks_per_split * 32);
+                for (long long kc = kbeg; kc < kend; kc += 32) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x500u | s)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), stage_tx);
-                    const uint32_t a_dst = base + s * kDwStageBytes;
-                    const uint32_t b_dst = a_dst + kDwABytes;
+                    const uint32_t a_dst = base + s * kGgStageBytes;
+                    const uint32_t b_dst = a_dst + kGgABytes;
+                    if (KIND == 0) {
 #pragma unroll
-                    for (int mb = 0; mb < 4; ++mb)
-                        tma_load_3d(a_dst + mb * kDwBoxBytes, &mapV, full_bar(s), cb * 128 + mb * 32, (int)pc, t);
-                    for (int nb = 0; nb < N / 32; ++nb)
-                        tma_load_3d(b_dst + nb * kDwBoxBytes, &mapM, full_bar(s), kb * N + nb * 32, (int)pc, t);
-                    if (++s == kDwStages) { s = 0; ph ^= 1u; }
+                        for (int mb = 0; mb < 4; ++mb)
+                            tma_load_3d(a_dst + mb * kGgBoxBytes, &mapA, full_bar(s), rb * 128 + mb * 32, (int)kc, t);
+                        for (int nb = 0; nb < N / 32; ++nb)
+                            tma_load_3d(b_dst + nb * kGgBoxBytes, &mapB, full_bar(s), cb * N + nb * 32, (int)kc, t);
+                    } else {
+                        tma_load_3d(a_dst, &mapA, full_bar(s), (int)kc, rb * 128, t);
+                        tma_load_3d(b_dst, &mapB, full_bar(s), (int)kc, cb * N, t);
+                    }
+                    if (++s == kGgStages) { s = 0; ph ^= 1u; }
                 }
             }
             if (!ok)
@@ -268,34 +270,35 @@ conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constan
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_tf32(128, N) | (1u << 15) | (1u << 16);   // A and B MN-major
+            const uint32_t idesc = make_idesc_tf32(128, N) | (KIND == 0 ? ((1u << 15) | (1u << 16)) : 0u);
             int s = 0; uint32_t ph = 0;
             uint32_t acc_use[2] = {0, 0};
             int buf = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
-                int split, t, cb, kb;
-                decode(u, split, t, cb, kb);
-                const long long pbeg = (long long)split * prm.chunks_per_split * 32;
-                const long long pend = min(prm.P, pbeg + (long long)prm.chunks_per_split * 32);
+                int split, t, rb, cb;
+                decode(u, split, t, rb, cb);
+                const long long kbeg = (long long)split * prm.chunks_per_split * 32;
+                const long long kend = min(prm.contr, kbeg + (long long)prm.chunks_per_split * 32);
                 if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x600u | buf)) { ok = false; break; }
                 acc_use[buf]++;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 256);
                 uint32_t first = 1;
-                for (long long pc = pbeg; pc < pend; pc += 32) {
+                for (long long kc = kbeg; kc < kend; kc += 32) {
                     if (!mbar_wait(full_bar(s), ph, abort_flag, 0x700u | s)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = base + s * kDwStageBytes;
-                    const uint64_t adesc = make_desc_mn_sw128(a_addr);
-                    const uint64_t bdesc = make_desc_mn_sw128(a_addr + kDwABytes);
+                    const uint32_t a_addr = base + s * kGgStageBytes;
+                    const uint64_t adesc = KIND == 0 ? make_desc_mn_sw128(a_addr) : make_desc_k_sw128(a_addr);
+                    const uint64_t bdesc = KIND == 0 ? make_desc_mn_sw128(a_addr + kGgABytes) : make_desc_k_sw128(a_addr + kGgABytes);
+                    const uint32_t step = KIND == 0 ? 64u : 2u;   // 1024 B / 32 B per 8 contraction steps
 #pragma unroll
-                    for (int kg = 0; kg < 4; ++kg) {   // next K group of 8 tiles: 1024 B further
-                        umma_tf32(d_tmem, adesc + 64u * kg, bdesc + 64u * kg, idesc, first ? 0u : 1u);
+                    for (int kg = 0; kg < 4; ++kg) {
+                        umma_tf32(d_tmem, adesc + step * kg, bdesc + step * kg, idesc, first ? 0u : 1u);
                         first = 0;
                     }
                     umma_commit(empty_bar(s));
-                    if (++s == kDwStages) { s = 0; ph ^= 1u; }
+                    if (++s == kGgStages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(accf_bar(buf));
                 buf ^= 1;
@@ -309,26 +312,40 @@ conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constan
         uint32_t acc_use[2] = {0, 0};
         int buf = 0;
         bool ok = true;
-        const long long plane_elems = (long long)16 * prm.C * prm.K;
+        const long long plane_elems = 16 * prm.rows * prm.cols;
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
-            int split, t, cb, kb;
-            decode(u, split, t, cb, kb);
-            if (!mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x800u | (ew << 4) | buf)) { ok = false; break; }
-            acc_use[buf]++;
-            tc_fence_after();
-            const int c = cb * 128 + q * 32 + lane;
-            const long long row_off = (prm.direct ? 0 : (long long)split * plane_elems) + ((long long)t * prm.C + c) * prm.K;
+            int split, t, rb, cb;
+            decode(u, split, t, rb, cb);
+            const bool use_mask = prm.mask && (KIND == 1 || prm.direct);
+            const long long row = (long long)rb * 128 + q * 32 + lane;
+            const long long row_off = (prm.direct ? 0 : (long long)split * plane_elems) + ((long long)t * prm.rows + row) * prm.cols;
             const int ncol_half = N / 2;
             for (int cc = 0; cc < ncol_half; cc += 32) {
                 const int col0 = half * ncol_half + cc;
-                const int k = kb * N + col0;
+                const int col = cb * N + col0;
+                const long long my_off = (row < prm.rows && col < prm.cols) ? row_off + col : -1;
+                const bool vec = (col + 32 <= prm.cols) && ((prm.cols & 3) == 0);
+                // offsets of the 8 lines this lane will store, and their mask values, fetched before the
+                // accumulator is even read so that the memory latency hides behind the TMEM load and the turn
+                long long off[8];
+                float4 mk[8];
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    off[rr] = __shfl_sync(0xffffffffu, my_off, 4 * rr + (lane >> 3));
+                    mk[rr] = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (vec && use_mask && off[rr] >= 0) mk[rr] = __ldg(reinterpret_cast<const float4 *>(prm.mask + off[rr] + 4 * (lane & 7)));
+                }
+                if (cc == 0) {   // first chunk of the unit: only now wait for the accumulator
+                    if (!mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x800u | (ew << 4) | buf)) { ok = false; break; }
+                    acc_use[buf]++;
+                    tc_fence_after();
+                }
                 float r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 256 + col0);
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) tmem_ld8(taddr + (uint32_t)(ch * 8), &r[ch * 8]);
                 tmem_ld_wait();
-                const long long my_off = (c < prm.C && k < prm.K) ? row_off + k : -1;
-                if (k + 32 <= prm.K && (prm.K & 3) == 0) {
+                if (vec) {
                     __syncwarp();
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8)
@@ -337,27 +354,29 @@ conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constan
                     __syncwarp();
 #pragma unroll
                     for (int rr = 0; rr < 8; ++rr) {
-                        const int row = 4 * rr + (lane >> 3), ch = lane & 7;
-                        const long long off = __shfl_sync(0xffffffffu, my_off, row);
-                        float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
-                        if (off >= 0) {
-                            if (prm.direct && prm.mask) {
-                                const float4 mk = __ldg(reinterpret_cast<const float4 *>(prm.mask + off + 4 * ch));
-                                v.x *= mk.x; v.y *= mk.y; v.z *= mk.z; v.w *= mk.w;
-                            }
-                            *reinterpret_cast<float4 *>(prm.out + off + 4 * ch) = v;
+                        const int srow = 4 * rr + (lane >> 3), ch = lane & 7;
+                        float4 v = *reinterpret_cast<const float4 *>(stg + srow * 32 + ((ch ^ (srow & 7)) << 2));
+                        if (off[rr] >= 0) {
+                            if (KIND == 0) { v.x *= mk[rr].x; v.y *= mk[rr].y; v.z *= mk[rr].z; v.w *= mk[rr].w; }
+                            else { v.x = mk[rr].x > 0.f ? v.x : 0.f; v.y = mk[rr].y > 0.f ? v.y : 0.f;
+                                   v.z = mk[rr].z > 0.f ? v.z : 0.f; v.w = mk[rr].w > 0.f ? v.w : 0.f; }
+                            *reinterpret_cast<float4 *>(prm.out + off[rr] + 4 * ch) = v;
                         }
                     }
                 } else if (my_off >= 0) {
 #pragma unroll
                     for (int x = 0; x < 32; ++x) {
-                        if (k + x >= prm.K) continue;
+                        if (col + x >= prm.cols) continue;
                         float v = r[x];
-                        if (prm.direct && prm.mask) v *= __ldg(prm.mask + my_off + x);
+                        if (use_mask) {
+                            const float m1 = __ldg(prm.mask + my_off + x);
+                            v = KIND == 0 ? v * m1 : (m1 > 0.f ? v : 0.f);
+                        }
                         prm.out[my_off + x] = v;
                     }
                 }
             }
+            if (!ok) break;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce_bar(buf));
@@ -373,28 +392,31 @@ conv_dw_tc_kernel(const __grid_constant__ CUtensorMap mapV, const __grid_constan
     }
 }
 
-// 3-D map over a (16, P, ch) fp32 tensor, ch contiguous: box = 32 channels x 32 rows, 128-B swizzle with 32-B atoms
-static bool make_map_dw(CUtensorMap *map, const float *ptr, int ch, long long rows)
+// 3-D map over a (16, rows, ch) fp32 tensor, ch contiguous.  mn_major: box = 32 channels x 32 rows with the
+// 32-B-atom 128-B swizzle; otherwise box = 32 channels x box_rows with the plain 128-B swizzle.
+static bool make_map_gg(CUtensorMap *map, const float *ptr, long long ch, long long rows, bool mn_major, int box_rows)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[3] = {(cuuint64_t)ch, (cuuint64_t)rows, 16};
     cuuint64_t strides[2] = {(cuuint64_t)ch * 4, (cuuint64_t)rows * ch * 4};
-    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t box[3] = {32, (cuuint32_t)(mn_major ? 32 : box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(ptr), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int dw_tc_cols(int K) { return K > 128 ? 256 : (K > 64 ? 128 : 64); }
+static int gg_cols(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
-// Splits of the P range: enough units for every SM, at least 8 chunks of 32 tiles per split
+// Splits of the P range for dW: enough units for every SM, at least 8 chunks of 32 tiles per split
 int conv_dw_tc_splits(long long P, int C, int K)
 {
-    const long long base_units = (long long)16 * cdiv(C, 128) * cdiv(K, dw_tc_cols(K));
+    const long long base_units = (long long)16 * cdiv(C, 128) * cdiv(K, gg_cols(K));
     const long long chunks = cdivll(P, 32);
-    long long s = cdivll(kNumSMs, base_units);
+    // one split when the unsplit units already cover most SMs: a second round plus the reduction pass
+    // would cost more than the idle SMs do
+    long long s = base_units * 3 >= kNumSMs * 2 ? 1 : cdivll(kNumSMs, base_units);
     const long long max_s = chunks / 8 > 0 ? chunks / 8 : 1;
     if (s > max_s) s = max_s;
     if (s < 1) s = 1;
@@ -402,32 +424,59 @@ int conv_dw_tc_splits(long long P, int C, int K)
     return (int)cdivll(chunks, cps);
 }
 
+template <int KIND>
+static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const GgParams &prm, cudaStream_t st)
+{
+    if (cudaFuncSetAttribute(conv_grad_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgSmemBytes) != cudaSuccess)
+        return WG2X2_ERR_LAUNCH;
+    const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
+    conv_grad_gemm_tc_kernel<KIND><<<grid, kTcThreads, kGgSmemBytes, st>>>(mapA, mapB, prm);
+    return launch_status();
+}
+
 int conv_dw_tc(const float *V, const float *dM, const float *mask, float *dW, float *partial, long long P, int C, int K,
                cudaStream_t st)
 {
-    DwParams prm;
-    prm.P = P; prm.C = C; prm.K = K;
-    prm.N = dw_tc_cols(K);
-    prm.nCB = cdiv(C, 128);
-    prm.nKB = cdiv(K, prm.N);
+    GgParams prm;
+    prm.rows = C; prm.cols = K; prm.contr = P;
+    prm.N = gg_cols(K);
+    prm.nRB = cdiv(C, 128);
+    prm.nCB = cdiv(K, prm.N);
     prm.splits = conv_dw_tc_splits(P, C, K);
     prm.chunks_per_split = (int)cdivll(cdivll(P, 32), prm.splits);
-    prm.units = 16 * prm.nCB * prm.nKB * prm.splits;
+    prm.units = 16 * prm.nRB * prm.nCB * prm.splits;
     prm.direct = prm.splits == 1;
     prm.out = prm.direct ? dW : partial;
     prm.mask = mask;
     CUtensorMap mapV, mapM;
-    if (!make_map_dw(&mapV, V, C, P) || !make_map_dw(&mapM, dM, K, P)) return WG2X2_ERR_LAUNCH;
-    if (cudaFuncSetAttribute(conv_dw_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDwSmemBytes) != cudaSuccess)
-        return WG2X2_ERR_LAUNCH;
-    const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
-    conv_dw_tc_kernel<<<grid, kTcThreads, kDwSmemBytes, st>>>(mapV, mapM, prm);
-    if (launch_status() != WG2X2_OK) return WG2X2_ERR_LAUNCH;
-    if (!prm.direct) {
-        const long long n = (long long)16 * C * K;
-        dw_reduce_launch(partial, mask, dW, n, prm.splits, st);
-    }
+    if (!make_map_gg(&mapV, V, C, P, true, 32) || !make_map_gg(&mapM, dM, K, P, true, 32)) return WG2X2_ERR_LAUNCH;
+    const int s = gg_launch<0>(mapV, mapM, prm, st);
+    if (s != WG2X2_OK) return s;
+    if (!prm.direct) dw_reduce_launch(partial, mask, dW, (long long)16 * C * K, prm.splits, st);
     return launch_status();
+}
+
+int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, float *dV, long long P, int C, int K, int relu,
+               cudaStream_t st)
+{
+    if (P > 0x7fffffffLL - 128) return WG2X2_ERR_UNSUPPORTED;
+    const long long n = (long long)16 * C * K;
+    round_tf32_kernel<<<(int)min((long long)kNumSMs * 8, cdivll(n, 256)), 256, 0, st>>>(Wt, Wr, n);
+    if (launch_status() != WG2X2_OK) return WG2X2_ERR_LAUNCH;
+    GgParams prm;
+    prm.rows = P; prm.cols = C; prm.contr = K;
+    prm.N = gg_cols(C);
+    prm.nRB = (int)cdivll(P, 128);
+    prm.nCB = cdiv(C, prm.N);
+    prm.splits = 1;
+    prm.chunks_per_split = cdiv(K, 32);
+    prm.units = 16 * prm.nRB * prm.nCB;
+    prm.direct = 1;
+    prm.out = dV;
+    prm.mask = relu ? V : nullptr;
+    CUtensorMap mapA, mapB;
+    if (!make_map_gg(&mapA, dM, K, P, false, 128) || !make_map_gg(&mapB, Wr, K, C, false, prm.N)) return WG2X2_ERR_LAUNCH;
+    return gg_launch<1>(mapA, mapB, prm, st);
 }
 
 size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW)
@@ -450,8 +499,7 @@ int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *m
     int s = launch_dm(dY, dM, B, H, W, K, layout, st);
     if (s != WG2X2_OK) return s;
     if (dV) {
-        s = conv_dv_tc(V, Wt, dM, reinterpret_cast<float *>(wsb + lay.wr), reinterpret_cast<unsigned long long *>(wsb + lay.masks),
-                       dV, P, C, K, relu, st);
+        s = conv_dv_tc(V, Wt, dM, reinterpret_cast<float *>(wsb + lay.wr), dV, P, C, K, relu, st);
         if (s != WG2X2_OK) return s;
     }
     if (dW) {

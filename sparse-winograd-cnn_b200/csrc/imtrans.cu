@@ -306,6 +306,44 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_kernel(const float *__re
     }
 }
 
+// NCHW, image rows up to 192 pixels: the same gather with lane = channel over a band of R tile rows;
+// the 2R x W output pixels of each channel collect in shared memory (odd pitch between channels) and
+// leave as one contiguous run per channel.
+template <bool MASK>
+__global__ void __launch_bounds__(256) imtrans_bwd_nchw_band_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                      float *__restrict__ dX, int B, int H, int W, int C, int nH,
+                                                                      int nW, int R, int nbands, int pitch)
+{
+    extern __shared__ float O[];   // [32 channels][pitch]
+    const int band = blockIdx.x % nbands;
+    const int b = blockIdx.x / nbands;
+    const int c0 = blockIdx.y * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int th0 = band * R;
+    const int rows_blk = min(R, nH - th0);
+    const long long plane = (long long)B * nH * nW * C;
+    const bool c_ok = c0 + lane < C;
+    for (int q = warp; q < rows_blk * nW; q += 8) {
+        const int br = q / nW, bw = q - br * nW;
+        float out[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        if (c_ok) imtrans_bwd_block<float, MASK>(dV, Vm, plane, b, th0 + br, bw, nH, nW, C, c0 + lane, out);
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (2 * bw + e < W) O[lane * pitch + (2 * br + a) * W + 2 * bw + e] = out[a][e];
+    }
+    __syncthreads();
+    const int lo = 2 * th0, hi = min(2 * th0 + 2 * rows_blk, H);
+    const int n = (hi - lo) * W;
+    for (int cc = warp; cc < 32; cc += 8) {
+        if (c0 + cc >= C) break;
+        float *dst = dX + (((long long)b * C + c0 + cc) * H + lo) * W;
+        const float *src = O + cc * pitch;
+        for (int i = lane; i < n; i += 32) dst[i] = src[i];
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
@@ -365,6 +403,26 @@ int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W
             else    imtrans_bwd_nhwc_kernel<1, false><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
         }
     } else {
+        if (W <= 192) {
+            int R = kBandFloats / (2 * W);
+            if (R < 1) R = 1;
+            if (R > nH) R = nH;
+            const int nbands = cdiv(nH, R);
+            const int pitch = (2 * R * W) | 1;
+            const int smem = 32 * pitch * (int)sizeof(float);
+            if ((long long)B * nbands > 0x7fffffffLL || cdiv(C, 32) > 65535) return WG2X2_ERR_UNSUPPORTED;
+            dim3 grid((unsigned)(B * nbands), cdiv(C, 32));
+            if (Vm) {
+                if (cudaFuncSetAttribute(imtrans_bwd_nchw_band_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                    return WG2X2_ERR_LAUNCH;
+                imtrans_bwd_nchw_band_kernel<true><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, R, nbands, pitch);
+            } else {
+                if (cudaFuncSetAttribute(imtrans_bwd_nchw_band_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                    return WG2X2_ERR_LAUNCH;
+                imtrans_bwd_nchw_band_kernel<false><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, R, nbands, pitch);
+            }
+            return launch_status();
+        }
         const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
         if (gx > 0x7fffffffLL || cdiv(C, kCCH) > 65535) return WG2X2_ERR_UNSUPPORTED;
         dim3 grid((unsigned)gx, cdiv(C, kCCH));
