@@ -55,6 +55,14 @@ int wg2x2_imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int 
                       void *stream);
 
 /*
+ * The same with a per-channel affine map applied to the pixels first, V = [relu](B^T (x*in_scale[c]+in_shift[c]) B),
+ * the zero padding staying zero.  It folds the inference-form BatchNorm that the reference graph places in front
+ * of every WinogradImTrans (ResNet-18-var/imagenet-resnet-transWino-prune.py:117-118) into the transform's load.
+ */
+int wg2x2_imtrans_fwd_affine(const float *X, const float *in_scale, const float *in_shift, float *V, int B, int H,
+                             int W, int C, int layout, int relu, void *stream);
+
+/*
  * Gradient of the input transform: dX = overlap-add of B g B^T over the tiles covering each
  * pixel.  dV is read, never written (the reference transforms it in place).  V_relu, when
  * not NULL, is the saved forward output of wg2x2_imtrans_fwd(relu=1): the gradient is taken
@@ -93,6 +101,15 @@ size_t wg2x2_prepared_weights_bytes(int C, int K);
 int wg2x2_weights_prepare(const float *Wt, int C, int K, void *prepared, size_t prepared_bytes, void *stream);
 int wg2x2_conv_fwd_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K,
                             int out_h, int out_w, int layout, void *stream);
+/*
+ * wg2x2_conv_fwd_prepared with the epilogue extras Y = acc*out_scale[k] + out_shift[k] (+ residual), each optional
+ * (NULL): the BatchNorm after a WinogradConv and the shortcut addition of a residual block
+ * (ResNet-18-var/imagenet-resnet-transWino-prune.py:122-128) done while the result is still in registers.
+ * `residual` has the shape and layout of Y.  out_scale/out_shift and residual must be 16-byte aligned.
+ */
+int wg2x2_conv_fwd_prepared_fused(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K,
+                                  int out_h, int out_w, int layout, const float *out_scale, const float *out_shift,
+                                  const float *residual, void *stream);
 
 /*
  * Gradient of the product/output-transform op for dY of size (B,H,W,K):

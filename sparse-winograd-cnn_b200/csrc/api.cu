@@ -4,7 +4,8 @@
 
 namespace wg {
 // imtrans.cu
-int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, cudaStream_t st);
+int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, const float *scale, const float *shift,
+                cudaStream_t st);
 int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W, int C, int layout, cudaStream_t st);
 // conv_ffma.cu
 int conv_fwd_ffma(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
@@ -23,7 +24,7 @@ int tc_last_device_status(cudaStream_t st, unsigned int *where);
 size_t prepared_weights_bytes(int C, int K);
 int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
-                         int layout, cudaStream_t st);
+                         int layout, const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
 size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW);
 int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *mask, float *dV, float *dW, int B, int H, int W,
                 int C, int K, int layout, int relu, void *ws, size_t ws_bytes, cudaStream_t st);
@@ -55,7 +56,14 @@ int wg2x2_abi_version(void) { return 1; }
 
 int wg2x2_imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, void *stream)
 {
-    return imtrans_fwd(X, V, B, H, W, C, layout, relu, (cudaStream_t)stream);
+    return imtrans_fwd(X, V, B, H, W, C, layout, relu, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int wg2x2_imtrans_fwd_affine(const float *X, const float *in_scale, const float *in_shift, float *V, int B, int H, int W, int C,
+                             int layout, int relu, void *stream)
+{
+    if (!in_scale || !in_shift) return WG2X2_ERR_BAD_ARG;
+    return imtrans_fwd(X, V, B, H, W, C, layout, relu, in_scale, in_shift, (cudaStream_t)stream);
 }
 
 int wg2x2_imtrans_bwd(const float *dV, const float *V_relu, float *dX, int B, int H, int W, int C, int layout, void *stream)
@@ -94,7 +102,17 @@ int wg2x2_conv_fwd_prepared(const float *V, const void *prepared, float *Y, int 
 {
     if (!V || !prepared || !Y || B <= 0 || nH <= 0 || nW <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
     if (!layout_ok(layout) || !crop_ok(out_h, nH) || !crop_ok(out_w, nW)) return WG2X2_ERR_BAD_ARG;
-    return conv_fwd_tc_prepared(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, (cudaStream_t)stream);
+    return conv_fwd_tc_prepared(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+
+int wg2x2_conv_fwd_prepared_fused(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int out_h,
+                                  int out_w, int layout, const float *out_scale, const float *out_shift, const float *residual,
+                                  void *stream)
+{
+    if (!V || !prepared || !Y || B <= 0 || nH <= 0 || nW <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!layout_ok(layout) || !crop_ok(out_h, nH) || !crop_ok(out_w, nW)) return WG2X2_ERR_BAD_ARG;
+    return conv_fwd_tc_prepared(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, out_scale, out_shift, residual,
+                                (cudaStream_t)stream);
 }
 
 size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int want_dW)

@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(256) pack_weights_kernel(const float *__restri
 // ---------------------------------------------------------------------------------------
 struct TcParams {
     float *Y;
+    // optional epilogue extras: Y = acc * out_scale[k] + out_shift[k] (+ residual, same shape and layout as Y)
+    const float *out_scale, *out_shift, *residual;
     const unsigned long long *masks;
     long long P;
     int nH, nW, C, K, outH, outW;
@@ -381,6 +383,11 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                     // Coalesced path: the warp turns its 32 tiles x 32 channels through shared memory
                     // so that 8 consecutive lanes write one full 128-byte line (4 lines per instruction).
                     float *stg = epi_stage_all + ew * (kEpiStageBytes / 4);
+                    float4 sc4 = make_float4(1.f, 1.f, 1.f, 1.f), sh4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (prm.out_scale) {   // this lane always stores channels kbase + 4*(lane&7) .. +3
+                        sc4 = __ldg(reinterpret_cast<const float4 *>(prm.out_scale + kbase) + (lane & 7));
+                        sh4 = __ldg(reinterpret_cast<const float4 *>(prm.out_shift + kbase) + (lane & 7));
+                    }
 #pragma unroll
                     for (int a = 0; a < 2; ++a)
 #pragma unroll
@@ -398,8 +405,18 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                             for (int r = 0; r < 8; ++r) {
                                 const int row = 4 * r + (lane >> 3), ch = lane & 7;
                                 const long long off = __shfl_sync(0xffffffffu, my_off, row);
-                                const float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
-                                if (off >= 0) *reinterpret_cast<float4 *>(prm.Y + off + 4 * ch) = v;
+                                float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
+                                if (off >= 0) {
+                                    if (prm.out_scale) {
+                                        v.x = fmaf(v.x, sc4.x, sh4.x); v.y = fmaf(v.y, sc4.y, sh4.y);
+                                        v.z = fmaf(v.z, sc4.z, sh4.z); v.w = fmaf(v.w, sc4.w, sh4.w);
+                                    }
+                                    if (prm.residual) {
+                                        const float4 rs = __ldg(reinterpret_cast<const float4 *>(prm.residual + off + 4 * ch));
+                                        v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
+                                    }
+                                    *reinterpret_cast<float4 *>(prm.Y + off + 4 * ch) = v;
+                                }
                             }
                         }
                 } else if (tile_ok) {
@@ -409,10 +426,15 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                         for (int e = 0; e < 2; ++e) {
                             const int h = 2 * th + a, w = 2 * tw + e;
                             if (h >= prm.outH || w >= prm.outW) continue;
-                            float *dst = prm.Y + (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase;
+                            const long long o = (((long long)b * prm.outH + h) * prm.outW + w) * prm.K + kbase;
 #pragma unroll
                             for (int c = 0; c < 32; ++c)
-                                if (kbase + c < prm.K) dst[c] = y[2 * a + e][c];
+                                if (kbase + c < prm.K) {
+                                    float v = y[2 * a + e][c];
+                                    if (prm.out_scale) v = fmaf(v, __ldg(prm.out_scale + kbase + c), __ldg(prm.out_shift + kbase + c));
+                                    if (prm.residual) v += __ldg(prm.residual + o + c);
+                                    prm.Y[o + c] = v;
+                                }
                         }
                 }
             } else if (tile_ok) {
@@ -426,12 +448,25 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         if (kbase + c >= prm.K) continue;
-                        float *dst = prm.Y + (((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + 2 * tw;
+                        const long long o = (((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + 2 * tw;
+                        float v0 = y[2 * a][c], v1 = y[2 * a + 1][c];
+                        if (prm.out_scale) {
+                            const float s1 = __ldg(prm.out_scale + kbase + c), b1 = __ldg(prm.out_shift + kbase + c);
+                            v0 = fmaf(v0, s1, b1); v1 = fmaf(v1, s1, b1);
+                        }
                         if (pair) {
-                            *reinterpret_cast<float2 *>(dst) = make_float2(y[2 * a][c], y[2 * a + 1][c]);
+                            if (prm.residual) {
+                                const float2 rs = __ldg(reinterpret_cast<const float2 *>(prm.residual + o));
+                                v0 += rs.x; v1 += rs.y;
+                            }
+                            *reinterpret_cast<float2 *>(prm.Y + o) = make_float2(v0, v1);
                         } else {
-                            dst[0] = y[2 * a][c];
-                            if (2 * tw + 1 < prm.outW) dst[1] = y[2 * a + 1][c];
+                            if (prm.residual) v0 += __ldg(prm.residual + o);
+                            prm.Y[o] = v0;
+                            if (2 * tw + 1 < prm.outW) {
+                                if (prm.residual) v1 += __ldg(prm.residual + o + 1);
+                                prm.Y[o + 1] = v1;
+                            }
                         }
                     }
                 }
@@ -515,11 +550,13 @@ int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes,
 // Launcher.  `contr` = contraction length C, `ncols` = output channels K; A is (16, P, contr), Bop is
 // (16, ncols, contr), both contraction-contiguous.
 static int tc_launch(int layout, const float *A, const float *Bop, const unsigned long long *masks, float *out, long long P,
-                     int nH, int nW, int contr, int ncols, int outH, int outW, cudaStream_t st)
+                     int nH, int nW, int contr, int ncols, int outH, int outW, const float *out_scale, const float *out_shift,
+                     const float *residual, cudaStream_t st)
 {
     if (P > 0x7fffffffLL - kBlockM) return WG2X2_ERR_UNSUPPORTED;
     TcParams prm;
     prm.Y = out;
+    prm.out_scale = out_scale; prm.out_shift = out_shift; prm.residual = residual;
     prm.masks = masks;
     prm.P = P; prm.nH = nH; prm.nW = nW; prm.C = contr; prm.K = ncols; prm.outH = outH; prm.outW = outW;
     prm.nKB = cdiv(ncols, kBlockN);
@@ -558,14 +595,18 @@ static int tc_launch(int layout, const float *A, const float *Bop, const unsigne
 }
 
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
-                         int layout, cudaStream_t st)
+                         int layout, const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st)
 {
     if (!V || !prepared || !Y) return WG2X2_ERR_BAD_ARG;
+    if ((out_scale == nullptr) != (out_shift == nullptr)) return WG2X2_ERR_BAD_ARG;
+    if (out_scale && ((reinterpret_cast<uintptr_t>(out_scale) & 15u) || (reinterpret_cast<uintptr_t>(out_shift) & 15u))) return WG2X2_ERR_BAD_ARG;
+    if (residual && (reinterpret_cast<uintptr_t>(residual) & 15u)) return WG2X2_ERR_BAD_ARG;
     if (!tc_shape_supported(C, K)) return WG2X2_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(V) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 15u)) return WG2X2_ERR_BAD_ARG;
     const unsigned long long *masks = reinterpret_cast<const unsigned long long *>(
         static_cast<const unsigned char *>(prepared) + align_up((size_t)16 * K * C * sizeof(float), 256));
-    return tc_launch(layout, V, static_cast<const float *>(prepared), masks, Y, (long long)B * nH * nW, nH, nW, C, K, outH, outW, st);
+    return tc_launch(layout, V, static_cast<const float *>(prepared), masks, Y, (long long)B * nH * nW, nH, nW, C, K, outH, outW,
+                     out_scale, out_shift, residual, st);
 }
 
 size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K)
@@ -582,7 +623,7 @@ int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW
     if (!ws || ws_bytes < prepared_weights_bytes(C, K)) return WG2X2_ERR_WORKSPACE;
     const int s = weights_prepare(Wt, C, K, ws, ws_bytes, st);
     if (s != WG2X2_OK) return s;
-    return conv_fwd_tc_prepared(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, st);
+    return conv_fwd_tc_prepared(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, nullptr, nullptr, nullptr, st);
 }
 
 void dw_reduce_launch(const float *partial, const float *mask, float *dW, long long n, int splits, cudaStream_t st);  // conv_ffma.cu

@@ -15,6 +15,8 @@ __device__ __forceinline__ float4 ldg(const float4 *p) { return __ldg(p); }
 __device__ __forceinline__ float ldg(const float *p) { return __ldg(p); }
 __device__ __forceinline__ float4 zero_of(float4) { return make_float4(0.f, 0.f, 0.f, 0.f); }
 __device__ __forceinline__ float zero_of(float) { return 0.f; }
+__device__ __forceinline__ float4 fma_of(float4 a, float4 s, float4 b) { return make_float4(fmaf(a.x, s.x, b.x), fmaf(a.y, s.y, b.y), fmaf(a.z, s.z, b.z), fmaf(a.w, s.w, b.w)); }
+__device__ __forceinline__ float fma_of(float a, float s, float b) { return fmaf(a, s, b); }
 __device__ __forceinline__ float4 relu_of(float4 a) { return make_float4(fmaxf(a.x, 0.f), fmaxf(a.y, 0.f), fmaxf(a.z, 0.f), fmaxf(a.w, 0.f)); }
 __device__ __forceinline__ float relu_of(float a) { return fmaxf(a, 0.f); }
 __device__ __forceinline__ float4 keep_where_pos(float4 g, float4 m) { return make_float4(m.x > 0.f ? g.x : 0.f, m.y > 0.f ? g.y : 0.f, m.z > 0.f ? g.z : 0.f, m.w > 0.f ? g.w : 0.f); }
@@ -26,7 +28,8 @@ __device__ __forceinline__ float keep_where_pos(float g, float m) { return m > 0
 // ------------------------------------------------------------------------------------------
 template <int VEC>
 __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__restrict__ X, float *__restrict__ V,
-                                                                 int B, int H, int W, int C, int nH, int nW, int relu)
+                                                                 int B, int H, int W, int C, int nH, int nW, int relu,
+                                                                 const float *__restrict__ scale, const float *__restrict__ shift)
 {
     using T = typename Vec<VEC>::type;
     const int CV = C / VEC;
@@ -40,6 +43,11 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__re
     const int b = (int)(p / ((long long)nW * nH));
 
     const T *Xv = reinterpret_cast<const T *>(X);
+    // optional per-channel affine map of the pixels (an inference-form BatchNorm in front of the
+    // transform); the zero padding stays zero
+    const bool affine = scale != nullptr;
+    T sc = zero_of(T()), sh = zero_of(T());
+    if (affine) { sc = ldg(reinterpret_cast<const T *>(scale) + cv); sh = ldg(reinterpret_cast<const T *>(shift) + cv); }
     T d[4][4];
 #pragma unroll
     for (int y = 0; y < 4; ++y) {
@@ -48,7 +56,9 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__re
         for (int x = 0; x < 4; ++x) {
             const int fx = 2 * tw - 1 + x;
             const bool in = (fy >= 0) && (fy < H) && (fx >= 0) && (fx < W);
-            d[y][x] = in ? ldg(Xv + (((long long)b * H + fy) * W + fx) * CV + cv) : zero_of(T());
+            T v = in ? ldg(Xv + (((long long)b * H + fy) * W + fx) * CV + cv) : zero_of(T());
+            if (affine && in) v = fma_of(v, sc, sh);
+            d[y][x] = v;
         }
     }
     T v[4][4];
@@ -75,7 +85,8 @@ constexpr int kRowPitch = 2 * kTSEG + 2;       // 66 pixels feed 32 tiles
 constexpr int kChanPitch = 4 * kRowPitch + 1;  // odd, so 32 channels hit 32 different banks
 
 __global__ void __launch_bounds__(256) imtrans_fwd_nchw_kernel(const float *__restrict__ X, float *__restrict__ V,
-                                                                 int B, int H, int W, int C, int nH, int nW, int relu)
+                                                                 int B, int H, int W, int C, int nH, int nW, int relu,
+                                                                 const float *__restrict__ scale, const float *__restrict__ shift)
 {
     __shared__ float S[kCCH * kChanPitch];
     const int nseg = cdiv(nW, kTSEG);
@@ -93,8 +104,10 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_kernel(const float *__re
         const int c = idx / (4 * kRowPitch);
         const int gx = 2 * tw0 - 1 + x, gy = 2 * th - 1 + y;
         float val = 0.f;
-        if (c0 + c < C && gx >= 0 && gx < W && gy >= 0 && gy < H)
+        if (c0 + c < C && gx >= 0 && gx < W && gy >= 0 && gy < H) {
             val = __ldg(X + (((long long)b * C + c0 + c) * H + gy) * W + gx);
+            if (scale) val = fmaf(val, __ldg(scale + c0 + c), __ldg(shift + c0 + c));
+        }
         S[c * kChanPitch + y * kRowPitch + x] = val;
     }
     __syncthreads();
@@ -134,7 +147,8 @@ constexpr int kBandFloats = 384;   // at most this many input floats per channel
 
 __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float *__restrict__ X, float *__restrict__ V,
                                                                       int B, int H, int W, int C, int nH, int nW, int relu,
-                                                                      int R, int nbands, int pitch)
+                                                                      int R, int nbands, int pitch,
+                                                                      const float *__restrict__ scale, const float *__restrict__ shift)
 {
     extern __shared__ float S[];   // [32 channels][pitch]
     const int band = blockIdx.x % nbands;
@@ -159,6 +173,9 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float 
     const bool c_ok = c0 + lane < C;
     const float *Sc = S + lane * pitch;
     const int ntiles = rows_tile * nW;
+    const bool affine = scale != nullptr;
+    const float sc = (affine && c_ok) ? __ldg(scale + c0 + lane) : 1.f;
+    const float sh = (affine && c_ok) ? __ldg(shift + c0 + lane) : 0.f;
     for (int q = warp; q < ntiles; q += 8) {
         const int tr = q / nW, tw = q - tr * nW;
         float d[4][4], v[4][4];
@@ -169,7 +186,8 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float 
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
                 const int gx = 2 * tw - 1 + x;
-                d[y][x] = (row_ok && gx >= 0 && gx < W && c_ok) ? Sc[(2 * tr + y) * W + gx] : 0.f;
+                const bool in = row_ok && gx >= 0 && gx < W && c_ok;
+                d[y][x] = in ? (affine ? fmaf(Sc[(2 * tr + y) * W + gx], sc, sh) : Sc[(2 * tr + y) * W + gx]) : 0.f;
             }
         }
         bt_d_b(d, v);
@@ -349,18 +367,20 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_band_kernel(const float 
 // ------------------------------------------------------------------------------------------
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, cudaStream_t st)
+int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout, int relu, const float *scale, const float *shift,
+                cudaStream_t st)
 {
     if (!X || !V || B <= 0 || H <= 0 || W <= 0 || C <= 0) return WG2X2_ERR_BAD_ARG;
+    if ((scale == nullptr) != (shift == nullptr)) return WG2X2_ERR_BAD_ARG;
     if (layout != WG2X2_NHWC && layout != WG2X2_NCHW) return WG2X2_ERR_BAD_ARG;
     const int nH = (H + 1) / 2, nW = (W + 1) / 2;
     if (layout == WG2X2_NHWC) {
-        if ((C % 4 == 0) && aligned16(X) && aligned16(V)) {
+        if ((C % 4 == 0) && aligned16(X) && aligned16(V) && (!scale || (aligned16(scale) && aligned16(shift)))) {
             const long long total = (long long)B * nH * nW * (C / 4);
-            imtrans_fwd_nhwc_kernel<4><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+            imtrans_fwd_nhwc_kernel<4><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         } else {
             const long long total = (long long)B * nH * nW * C;
-            imtrans_fwd_nhwc_kernel<1><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+            imtrans_fwd_nhwc_kernel<1><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         }
     } else {
         const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
@@ -378,9 +398,9 @@ int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout
             if (cudaFuncSetAttribute(imtrans_fwd_nchw_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
                 return WG2X2_ERR_LAUNCH;
             imtrans_fwd_nchw_band_kernel<<<dim3((unsigned)gxb, cdiv(C, 32)), 256, smem, st>>>(X, V, B, H, W, C, nH, nW, relu, R,
-                                                                                               nbands, pitch);
+                                                                                               nbands, pitch, scale, shift);
         } else {
-            imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu);
+            imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         }
     }
     return launch_status();

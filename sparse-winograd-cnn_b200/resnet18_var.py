@@ -56,14 +56,26 @@ class _WinogradLayer(torch.nn.Module):
         self.cout = cout
         self._prepared = None
 
+    def prepared(self):
+        if self._prepared is None or self._prepared.device != self.W.device:
+            self._prepared = wg2x2.prepare_weights(self.W)
+        return self._prepared
+
     def forward(self, x, math="tf32"):
         B, C, H, W = x.shape
         v = wg2x2.imtrans_fwd(x.contiguous(), relu=True, layout="NCHW")
         if math == "tf32":
-            if self._prepared is None or self._prepared.device != x.device:
-                self._prepared = wg2x2.prepare_weights(self.W)
-            return wg2x2.conv_fwd_prepared(v, self._prepared, self.cout, H, W, layout="NCHW")
+            return wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout="NCHW")
         return wg2x2.conv_fwd(v, self.W, H, W, layout="NCHW", math="fp32")
+
+    def forward_fused(self, x, bn_in, bn_out=None, residual=None):
+        """BatchNorm -> transform + ReLU -> product [-> BatchNorm + shortcut add] in two kernels: bn_in folds
+        into the transform's load, bn_out and the residual into the product's epilogue (tensor-core path)."""
+        B, C, H, W = x.shape
+        v = wg2x2.imtrans_fwd(x.contiguous(), relu=True, layout="NCHW", in_scale=bn_in.scale, in_shift=bn_in.shift)
+        return wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout="NCHW",
+                                       out_scale=None if bn_out is None else bn_out.scale,
+                                       out_shift=None if bn_out is None else bn_out.shift, residual=residual)
 
     def forward_reference(self, x):
         """The same layer from the transform matrices with float64 einsums (for tests)."""
@@ -80,10 +92,11 @@ class _WinogradLayer(torch.nn.Module):
 
 
 class ResNet18Var(torch.nn.Module):
-    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32"):
+    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32", fused=True):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
         self.math = math
+        self.fused = fused      # fold BatchNorms and shortcut additions into the Winograd kernels (tensor-core path)
         self.stage5_pool = stage5_pool
         self.stem = torch.nn.Parameter(torch.randn((64, 3, 7, 7), generator=gen) * (2.0 / (49 * 64)) ** 0.5, requires_grad=False)
         self.blocks = torch.nn.ModuleList()
@@ -101,11 +114,15 @@ class ResNet18Var(torch.nn.Module):
         self.fc_w = torch.nn.Parameter(torch.randn((num_classes, 512), generator=gen) * (1.0 / 512) ** 0.5, requires_grad=False)
         self.fc_b = torch.nn.Parameter(torch.zeros(num_classes), requires_grad=False)
 
-    def _branch(self, blk, l, ref):
+    def _block(self, blk, l, main, ref):
+        """main + bn2c(conv(bn2b(conv(bn2a(l))))) with the Winograd layers as `ref` says."""
+        if not ref and self.math == "tf32" and self.fused:
+            t = blk["w2a"].forward_fused(l, blk["bn2a"])
+            return blk["w2b"].forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main.contiguous())
         conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math))
         t = conv(blk["w2a"], blk["bn2a"](l))
         t = conv(blk["w2b"], blk["bn2b"](t))
-        return blk["bn2c"](t)
+        return main + blk["bn2c"](t)
 
     def forward(self, image, reference=False):
         """image: (B,3,H,W) float32, already normalised.  reference=True computes the Winograd layers with
@@ -113,11 +130,13 @@ class ResNet18Var(torch.nn.Module):
         l = F.conv2d(F.pad(image, (2, 3, 2, 3)), self.stem, stride=2)   # 7x7/2 with TensorFlow's SAME padding
         l = _same_pool(l)
         for s, (blk_a, blk_b) in enumerate(self.blocks):
-            bra = self._branch(blk_a, l, reference)
             main = torch.relu(blk_a["pre"](l)) if s == 0 else torch.relu(l)
-            l = blk_a["bn1"](F.conv2d(main, blk_a.short)) + bra
-            bra = self._branch(blk_b, l, reference)
-            l = torch.relu(l) + bra
+            if reference or not self.fused:
+                main = blk_a["bn1"](F.conv2d(main, blk_a.short))
+            else:   # the BatchNorm after the 1x1 shortcut folds into its weights and bias
+                main = F.conv2d(main, blk_a.short * blk_a["bn1"].scale.view(-1, 1, 1, 1), bias=blk_a["bn1"].shift)
+            l = self._block(blk_a, l, main, reference)
+            l = self._block(blk_b, l, torch.relu(l), reference)
             if s < 2 or (s == 2 and self.stage5_pool):
                 l = _same_pool(l)
         l = torch.relu(l).mean(dim=(2, 3))

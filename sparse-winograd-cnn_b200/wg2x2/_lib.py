@@ -33,12 +33,14 @@ _SIGS = {
     "wg2x2_status_string": (ctypes.c_char_p, [_i]),
     "wg2x2_abi_version": (_i, []),
     "wg2x2_imtrans_fwd": (_i, [_p, _p, _i, _i, _i, _i, _i, _i, _p]),
+    "wg2x2_imtrans_fwd_affine": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),
     "wg2x2_imtrans_bwd": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "wg2x2_conv_fwd": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i]),
     "wg2x2_prepared_weights_bytes": (_z, [_i, _i]),
     "wg2x2_weights_prepare": (_i, [_p, _i, _i, _p, _z, _p]),
     "wg2x2_conv_fwd_prepared": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
+    "wg2x2_conv_fwd_prepared_fused": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
     "wg2x2_conv_bwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_conv_bwd_dw_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),

@@ -39,14 +39,19 @@ def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device) if nbytes else None
 
 
-def imtrans_fwd(x, relu=False, layout="NHWC", out=None):
-    """x (B,H,W,C) or (B,C,H,W) -> V (16,B,nH,nW,C)."""
+def imtrans_fwd(x, relu=False, layout="NHWC", out=None, in_scale=None, in_shift=None):
+    """x (B,H,W,C) or (B,C,H,W) -> V (16,B,nH,nW,C); in_scale/in_shift (C,) apply x*scale+shift to the pixels first."""
     layout = _LAYOUTS[layout]
     _chk(x, "x")
     B, H, W, C = _img_dims(x, layout)
     V = out if out is not None else torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(lib.wg2x2_imtrans_fwd(_ptr(x), _ptr(V), B, H, W, C, layout, int(bool(relu)), _stream()), "wg2x2_imtrans_fwd")
+        if in_scale is not None:
+            _chk(in_scale, "in_scale"); _chk(in_shift, "in_shift")
+            _lib.check(lib.wg2x2_imtrans_fwd_affine(_ptr(x), _ptr(in_scale), _ptr(in_shift), _ptr(V), B, H, W, C, layout,
+                                                    int(bool(relu)), _stream()), "wg2x2_imtrans_fwd_affine")
+        else:
+            _lib.check(lib.wg2x2_imtrans_fwd(_ptr(x), _ptr(V), B, H, W, C, layout, int(bool(relu)), _stream()), "wg2x2_imtrans_fwd")
     return V
 
 
@@ -96,8 +101,10 @@ def prepare_weights(Wt):
     return buf
 
 
-def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out=None):
-    """As conv_fwd(math="tf32") with weights already prepared by prepare_weights."""
+def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out=None, out_scale=None, out_shift=None,
+                      residual=None):
+    """As conv_fwd(math="tf32") with weights already prepared by prepare_weights; optionally
+    Y = acc*out_scale[k] + out_shift[k] + residual in the kernel's epilogue."""
     layout = _LAYOUTS[layout]
     _chk(V, "V")
     _, B, nH, nW, C = V.shape
@@ -105,8 +112,17 @@ def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out
     out_w = 2 * nW if out_w is None else out_w
     Y = out if out is not None else torch.empty(_img_shape(B, out_h, out_w, K, layout), dtype=torch.float32, device=V.device)
     with torch.cuda.device(V.device):
-        _lib.check(lib.wg2x2_conv_fwd_prepared(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
-                                               _stream()), "wg2x2_conv_fwd_prepared")
+        if out_scale is None and residual is None:
+            _lib.check(lib.wg2x2_conv_fwd_prepared(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
+                                                   _stream()), "wg2x2_conv_fwd_prepared")
+        else:
+            if residual is not None:
+                _chk(residual, "residual")
+                if residual.shape != Y.shape:
+                    raise ValueError("residual must have the shape of the output")
+            _lib.check(lib.wg2x2_conv_fwd_prepared_fused(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
+                                                         _ptr(out_scale), _ptr(out_shift), _ptr(residual), _stream()),
+                       "wg2x2_conv_fwd_prepared_fused")
     return Y
 
 

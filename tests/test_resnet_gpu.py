@@ -6,12 +6,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("math,tol", [("fp32", 2e-4), ("tf32", 2e-2)])
+@pytest.mark.parametrize("math,tol,fused", [("fp32", 2e-4, False), ("tf32", 2e-2, False), ("tf32", 2e-2, True)])
 @pytest.mark.parametrize("stage5_pool", [True, False])
-def test_forward_matches_einsum_graph(math, tol, stage5_pool):
+def test_forward_matches_einsum_graph(math, tol, fused, stage5_pool):
     from resnet18_var import ResNet18Var
     torch.manual_seed(0)
-    model = ResNet18Var(stage5_pool=stage5_pool, seed=3, math=math).cuda().eval()
+    model = ResNet18Var(stage5_pool=stage5_pool, seed=3, math=math, fused=fused).cuda().eval()
     x = torch.randn((2, 3, 96, 96), device="cuda")       # 24x24 at stage 2 ... 3x3 (odd) at stage 5
     with torch.no_grad():
         got = model(x)

@@ -152,3 +152,29 @@ def test_conv_bwd_tf32(wg, oracle, shape, layout):
     none, dW2 = wg.conv_bwd(_dev(V), _dev(Wm), _dev(dyl), layout=layout, math="tf32", need_dV=False)
     assert none is None and oracle.max_rel(dW2.cpu().numpy(), oracle.conv_bwd(V, Wm, dY)[1]) <= TOL_TF32
     _status_ok(wg)
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("shape", [(2, 14, 14, 64, 64), (2, 7, 7, 64, 128), (2, 9, 13, 36, 20), (1, 28, 28, 128, 96)])
+def test_fused_affine_and_residual(wg, oracle, shape, layout):
+    """Input affine folded into the transform, output affine + residual folded into the product's epilogue."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    rng = np.random.default_rng(5)
+    s_in, b_in = (1 + 0.2 * rng.standard_normal(C)).astype(np.float32), (0.3 * rng.standard_normal(C)).astype(np.float32)
+    s_out, b_out = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32), (0.3 * rng.standard_normal(K)).astype(np.float32)
+    R = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    to_l = (lambda a: a) if layout == "NHWC" else (lambda a: np.ascontiguousarray(np.transpose(a, (0, 3, 1, 2))))
+    V = wg.imtrans_fwd(_dev(to_l(X)), relu=True, layout=layout, in_scale=_dev(s_in), in_shift=_dev(b_in))
+    Vo = oracle.imtrans_fwd(X.astype(np.float64) * s_in + b_in, relu=True)
+    assert oracle.max_rel(V.cpu().numpy(), Vo) <= 1e-5
+    prepared = wg.prepare_weights(_dev(Wt))
+    want = oracle.conv_fwd(Vo, Wt, H, W) * s_out + b_out + R
+    for kw in (dict(out_scale=_dev(s_out), out_shift=_dev(b_out), residual=_dev(to_l(R))),):
+        Y = wg.conv_fwd_prepared(V, prepared, K, H, W, layout=layout, **kw).cpu().numpy()
+        got = Y if layout == "NHWC" else np.transpose(Y, (0, 2, 3, 1))
+        assert oracle.max_rel(got, want) <= TOL_TF32
+    Y2 = wg.conv_fwd_prepared(V, prepared, K, H, W, layout=layout, residual=_dev(to_l(R))).cpu().numpy()
+    got2 = Y2 if layout == "NHWC" else np.transpose(Y2, (0, 2, 3, 1))
+    assert oracle.max_rel(got2, oracle.conv_fwd(Vo, Wt, H, W) + R) <= TOL_TF32
+    _status_ok(wg)
