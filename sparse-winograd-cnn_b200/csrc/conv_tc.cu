@@ -8,8 +8,10 @@
 // (512 columns), so the epilogue of row i overlaps the MMAs of row i+1 and V is read from
 // memory exactly once per 64 output channels.  Nothing but Y is written.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2..9 = epilogue (two warps per TMEM lane quarter, 32 columns each).
+// Warp roles (384 threads = 3 warpgroups): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer
+// (warps 2-3 idle), warps 4..11 = epilogue (two warps per TMEM lane quarter, 32 columns each).  The
+// control warpgroup hands most of its registers to the epilogue warpgroups (setmaxnreg), which keep
+// 128 output values per thread live.
 // Every mbarrier wait is bounded; on expiry the kernel records where it gave up, drains
 // and returns (status readable through wg2x2_last_device_status).
 #include <cuda.h>
@@ -26,7 +28,8 @@ constexpr int kStages = 8;
 constexpr int kABytes = kBlockM * kBlockK * 4;   // 16 KB
 constexpr int kBBytes = kBlockN * kBlockK * 4;   //  8 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kTcThreads = 320;
+constexpr int kTcThreads = 320;           // gradient GEMM kernels: producer, MMA issuer, 8 epilogue warps
+constexpr int kFwdThreads = 384;          // forward kernel: one control warpgroup + two epilogue warpgroups
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kCtrlBytes = 1024;                   // barriers, TMEM pointer, abort flag, per-role block masks
@@ -214,8 +217,10 @@ struct TcParams {
     int units;
 };
 
-template <int LAYOUT>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// EXTRAS: compile the optional epilogue affine map and residual addition in (kept out of the plain kernel,
+// whose store loops are the critical path of the HBM-bound shapes).
+template <int LAYOUT, bool EXTRAS>
+__global__ void __launch_bounds__(kFwdThreads, 1)
 conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -253,6 +258,10 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 
     const int nCC = prm.nCC;
 
+    // 384 threads x 168 registers at launch: the control warpgroup drops to 40 registers per thread and the
+    // two epilogue warpgroups rise to 232 (each inside its own branch, so that no code is shared between them)
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------------
         if (lane == 0) {
@@ -324,9 +333,11 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 }
             }
         }
+    }
     } else {
         // ------------------------------ epilogue ----------------------------------------
-        const int ew = warp - 2;
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int ew = warp - 4;
         const int q = warp & 3;            // TMEM lane quarter this warp may read
         const int half = ew >> 2;          // which 32 of the 64 columns
         uint32_t acc_use[2] = {0, 0};
@@ -384,7 +395,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                     // so that 8 consecutive lanes write one full 128-byte line (4 lines per instruction).
                     float *stg = epi_stage_all + ew * (kEpiStageBytes / 4);
                     float4 sc4 = make_float4(1.f, 1.f, 1.f, 1.f), sh4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (prm.out_scale) {   // this lane always stores channels kbase + 4*(lane&7) .. +3
+                    if (EXTRAS && prm.out_scale) {   // this lane always stores channels kbase + 4*(lane&7) .. +3
                         sc4 = __ldg(reinterpret_cast<const float4 *>(prm.out_scale + kbase) + (lane & 7));
                         sh4 = __ldg(reinterpret_cast<const float4 *>(prm.out_shift + kbase) + (lane & 7));
                     }
@@ -401,21 +412,26 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                                 *reinterpret_cast<float4 *>(stg + lane * 32 + ((c8 ^ (lane & 7)) << 2)) =
                                     make_float4(y[2 * a + e][4 * c8], y[2 * a + e][4 * c8 + 1], y[2 * a + e][4 * c8 + 2], y[2 * a + e][4 * c8 + 3]);
                             __syncwarp();
+                            // residual values first (8 independent loads in flight), then the stores
+                            long long off[8];
+                            float4 rs[8];
+#pragma unroll
+                            for (int r = 0; r < 8; ++r) {
+                                off[r] = __shfl_sync(0xffffffffu, my_off, 4 * r + (lane >> 3));
+                                rs[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (EXTRAS && prm.residual && off[r] >= 0) rs[r] = __ldg(reinterpret_cast<const float4 *>(prm.residual + off[r]) + (lane & 7));
+                            }
 #pragma unroll
                             for (int r = 0; r < 8; ++r) {
                                 const int row = 4 * r + (lane >> 3), ch = lane & 7;
-                                const long long off = __shfl_sync(0xffffffffu, my_off, row);
                                 float4 v = *reinterpret_cast<const float4 *>(stg + row * 32 + ((ch ^ (row & 7)) << 2));
-                                if (off >= 0) {
-                                    if (prm.out_scale) {
+                                if (off[r] >= 0) {
+                                    if (EXTRAS && prm.out_scale) {
                                         v.x = fmaf(v.x, sc4.x, sh4.x); v.y = fmaf(v.y, sc4.y, sh4.y);
                                         v.z = fmaf(v.z, sc4.z, sh4.z); v.w = fmaf(v.w, sc4.w, sh4.w);
                                     }
-                                    if (prm.residual) {
-                                        const float4 rs = __ldg(reinterpret_cast<const float4 *>(prm.residual + off + 4 * ch));
-                                        v.x += rs.x; v.y += rs.y; v.z += rs.z; v.w += rs.w;
-                                    }
-                                    *reinterpret_cast<float4 *>(prm.Y + off + 4 * ch) = v;
+                                    if (EXTRAS) { v.x += rs[r].x; v.y += rs[r].y; v.z += rs[r].z; v.w += rs[r].w; }
+                                    *reinterpret_cast<float4 *>(prm.Y + off[r] + 4 * ch) = v;
                                 }
                             }
                         }
@@ -431,8 +447,8 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                             for (int c = 0; c < 32; ++c)
                                 if (kbase + c < prm.K) {
                                     float v = y[2 * a + e][c];
-                                    if (prm.out_scale) v = fmaf(v, __ldg(prm.out_scale + kbase + c), __ldg(prm.out_shift + kbase + c));
-                                    if (prm.residual) v += __ldg(prm.residual + o + c);
+                                    if (EXTRAS && prm.out_scale) v = fmaf(v, __ldg(prm.out_scale + kbase + c), __ldg(prm.out_shift + kbase + c));
+                                    if (EXTRAS && prm.residual) v += __ldg(prm.residual + o + c);
                                     prm.Y[o + c] = v;
                                 }
                         }
@@ -445,28 +461,33 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 for (int a = 0; a < 2; ++a) {
                     const int h = 2 * th + a;
                     if (h >= prm.outH) continue;
+                    const long long cstride = (long long)prm.outH * prm.outW;
+                    const long long o0 = (((long long)b * prm.K + kbase) * prm.outH + h) * prm.outW + 2 * tw;
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        if (kbase + c >= prm.K) continue;
-                        const long long o = (((long long)b * prm.K + kbase + c) * prm.outH + h) * prm.outW + 2 * tw;
-                        float v0 = y[2 * a][c], v1 = y[2 * a + 1][c];
-                        if (prm.out_scale) {
-                            const float s1 = __ldg(prm.out_scale + kbase + c), b1 = __ldg(prm.out_shift + kbase + c);
-                            v0 = fmaf(v0, s1, b1); v1 = fmaf(v1, s1, b1);
+                    for (int cg = 0; cg < 32; cg += 8) {
+                        // residual values of 8 channels first (independent loads in flight), then the stores
+                        float2 rs[8];
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            rs[c] = make_float2(0.f, 0.f);
+                            if (EXTRAS && prm.residual && kbase + cg + c < prm.K) {
+                                const float *rp = prm.residual + o0 + (cg + c) * cstride;
+                                if (pair) rs[c] = __ldg(reinterpret_cast<const float2 *>(rp));
+                                else { rs[c].x = __ldg(rp); if (2 * tw + 1 < prm.outW) rs[c].y = __ldg(rp + 1); }
+                            }
                         }
-                        if (pair) {
-                            if (prm.residual) {
-                                const float2 rs = __ldg(reinterpret_cast<const float2 *>(prm.residual + o));
-                                v0 += rs.x; v1 += rs.y;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            if (kbase + cg + c >= prm.K) continue;
+                            float v0 = y[2 * a][cg + c], v1 = y[2 * a + 1][cg + c];
+                            if (EXTRAS && prm.out_scale) {
+                                const float s1 = __ldg(prm.out_scale + kbase + cg + c), b1 = __ldg(prm.out_shift + kbase + cg + c);
+                                v0 = fmaf(v0, s1, b1); v1 = fmaf(v1, s1, b1);
                             }
-                            *reinterpret_cast<float2 *>(prm.Y + o) = make_float2(v0, v1);
-                        } else {
-                            if (prm.residual) v0 += __ldg(prm.residual + o);
-                            prm.Y[o] = v0;
-                            if (2 * tw + 1 < prm.outW) {
-                                if (prm.residual) v1 += __ldg(prm.residual + o + 1);
-                                prm.Y[o + 1] = v1;
-                            }
+                            if (EXTRAS) { v0 += rs[c].x; v1 += rs[c].y; }
+                            float *dst = prm.Y + o0 + (cg + c) * cstride;
+                            if (pair) *reinterpret_cast<float2 *>(dst) = make_float2(v0, v1);
+                            else { dst[0] = v0; if (2 * tw + 1 < prm.outW) dst[1] = v1; }
                         }
                     }
                 }
@@ -581,15 +602,16 @@ static int tc_launch(int layout, const float *A, const float *Bop, const unsigne
     if (!make_map(&mapA, A, contr, P, kBlockM)) return WG2X2_ERR_LAUNCH;
     if (!make_map(&mapB, Bop, contr, ncols, kBlockN)) return WG2X2_ERR_LAUNCH;
     const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
-#define WG_TC_LAUNCH(L)                                                                                                 \
+#define WG_TC_LAUNCH(L, X)                                                                                              \
     do {                                                                                                                \
-        if (cudaFuncSetAttribute(conv_fwd_tc_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=     \
+        if (cudaFuncSetAttribute(conv_fwd_tc_kernel<L, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=  \
             cudaSuccess)                                                                                                \
             return WG2X2_ERR_LAUNCH;                                                                                    \
-        conv_fwd_tc_kernel<L><<<grid, kTcThreads, kSmemBytes, st>>>(mapA, mapB, prm);                                   \
+        conv_fwd_tc_kernel<L, X><<<grid, kFwdThreads, kSmemBytes, st>>>(mapA, mapB, prm);                               \
     } while (0)
-    if (layout == WG2X2_NHWC) WG_TC_LAUNCH(WG2X2_NHWC);
-    else WG_TC_LAUNCH(WG2X2_NCHW);
+    const bool extras = out_scale || residual;
+    if (layout == WG2X2_NHWC) { if (extras) WG_TC_LAUNCH(WG2X2_NHWC, true); else WG_TC_LAUNCH(WG2X2_NHWC, false); }
+    else                      { if (extras) WG_TC_LAUNCH(WG2X2_NCHW, true); else WG_TC_LAUNCH(WG2X2_NCHW, false); }
 #undef WG_TC_LAUNCH
     return launch_status();
 }

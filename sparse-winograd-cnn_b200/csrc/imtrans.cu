@@ -26,7 +26,7 @@ __device__ __forceinline__ float keep_where_pos(float g, float m) { return m > 0
 // Forward, NHWC.  One thread = one tile x VEC channels; consecutive threads walk the channel
 // axis first, so each of the 16 plane stores of a warp is one contiguous run.
 // ------------------------------------------------------------------------------------------
-template <int VEC>
+template <int VEC, bool AFFINE>
 __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__restrict__ X, float *__restrict__ V,
                                                                  int B, int H, int W, int C, int nH, int nW, int relu,
                                                                  const float *__restrict__ scale, const float *__restrict__ shift)
@@ -45,9 +45,8 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__re
     const T *Xv = reinterpret_cast<const T *>(X);
     // optional per-channel affine map of the pixels (an inference-form BatchNorm in front of the
     // transform); the zero padding stays zero
-    const bool affine = scale != nullptr;
     T sc = zero_of(T()), sh = zero_of(T());
-    if (affine) { sc = ldg(reinterpret_cast<const T *>(scale) + cv); sh = ldg(reinterpret_cast<const T *>(shift) + cv); }
+    if (AFFINE) { sc = ldg(reinterpret_cast<const T *>(scale) + cv); sh = ldg(reinterpret_cast<const T *>(shift) + cv); }
     T d[4][4];
 #pragma unroll
     for (int y = 0; y < 4; ++y) {
@@ -57,7 +56,7 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nhwc_kernel(const float *__re
             const int fx = 2 * tw - 1 + x;
             const bool in = (fy >= 0) && (fy < H) && (fx >= 0) && (fx < W);
             T v = in ? ldg(Xv + (((long long)b * H + fy) * W + fx) * CV + cv) : zero_of(T());
-            if (affine && in) v = fma_of(v, sc, sh);
+            if (AFFINE && in) v = fma_of(v, sc, sh);
             d[y][x] = v;
         }
     }
@@ -145,6 +144,7 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_kernel(const float *__re
 // ------------------------------------------------------------------------------------------
 constexpr int kBandFloats = 384;   // at most this many input floats per channel in shared memory
 
+template <bool AFFINE>
 __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float *__restrict__ X, float *__restrict__ V,
                                                                       int B, int H, int W, int C, int nH, int nW, int relu,
                                                                       int R, int nbands, int pitch,
@@ -173,9 +173,8 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float 
     const bool c_ok = c0 + lane < C;
     const float *Sc = S + lane * pitch;
     const int ntiles = rows_tile * nW;
-    const bool affine = scale != nullptr;
-    const float sc = (affine && c_ok) ? __ldg(scale + c0 + lane) : 1.f;
-    const float sh = (affine && c_ok) ? __ldg(shift + c0 + lane) : 0.f;
+    const float sc = (AFFINE && c_ok) ? __ldg(scale + c0 + lane) : 1.f;
+    const float sh = (AFFINE && c_ok) ? __ldg(shift + c0 + lane) : 0.f;
     for (int q = warp; q < ntiles; q += 8) {
         const int tr = q / nW, tw = q - tr * nW;
         float d[4][4], v[4][4];
@@ -187,7 +186,7 @@ __global__ void __launch_bounds__(256) imtrans_fwd_nchw_band_kernel(const float 
             for (int x = 0; x < 4; ++x) {
                 const int gx = 2 * tw - 1 + x;
                 const bool in = row_ok && gx >= 0 && gx < W && c_ok;
-                d[y][x] = in ? (affine ? fmaf(Sc[(2 * tr + y) * W + gx], sc, sh) : Sc[(2 * tr + y) * W + gx]) : 0.f;
+                d[y][x] = in ? (AFFINE ? fmaf(Sc[(2 * tr + y) * W + gx], sc, sh) : Sc[(2 * tr + y) * W + gx]) : 0.f;
             }
         }
         bt_d_b(d, v);
@@ -377,10 +376,14 @@ int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout
     if (layout == WG2X2_NHWC) {
         if ((C % 4 == 0) && aligned16(X) && aligned16(V) && (!scale || (aligned16(scale) && aligned16(shift)))) {
             const long long total = (long long)B * nH * nW * (C / 4);
-            imtrans_fwd_nhwc_kernel<4><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
+            const unsigned g = (unsigned)cdivll(total, 256);
+            if (scale) imtrans_fwd_nhwc_kernel<4, true><<<g, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
+            else       imtrans_fwd_nhwc_kernel<4, false><<<g, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         } else {
             const long long total = (long long)B * nH * nW * C;
-            imtrans_fwd_nhwc_kernel<1><<<(unsigned)cdivll(total, 256), 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
+            const unsigned g = (unsigned)cdivll(total, 256);
+            if (scale) imtrans_fwd_nhwc_kernel<1, true><<<g, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
+            else       imtrans_fwd_nhwc_kernel<1, false><<<g, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         }
     } else {
         const long long gx = (long long)B * nH * cdiv(nW, kTSEG);
@@ -395,10 +398,16 @@ int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout
             const int smem = 32 * pitch * (int)sizeof(float);
             const long long gxb = (long long)B * nbands;
             if (gxb > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
-            if (cudaFuncSetAttribute(imtrans_fwd_nchw_band_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                return WG2X2_ERR_LAUNCH;
-            imtrans_fwd_nchw_band_kernel<<<dim3((unsigned)gxb, cdiv(C, 32)), 256, smem, st>>>(X, V, B, H, W, C, nH, nW, relu, R,
-                                                                                               nbands, pitch, scale, shift);
+            const dim3 gb((unsigned)gxb, cdiv(C, 32));
+            if (scale) {
+                if (cudaFuncSetAttribute(imtrans_fwd_nchw_band_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                    return WG2X2_ERR_LAUNCH;
+                imtrans_fwd_nchw_band_kernel<true><<<gb, 256, smem, st>>>(X, V, B, H, W, C, nH, nW, relu, R, nbands, pitch, scale, shift);
+            } else {
+                if (cudaFuncSetAttribute(imtrans_fwd_nchw_band_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                    return WG2X2_ERR_LAUNCH;
+                imtrans_fwd_nchw_band_kernel<false><<<gb, 256, smem, st>>>(X, V, B, H, W, C, nH, nW, relu, R, nbands, pitch, scale, shift);
+            }
         } else {
             imtrans_fwd_nchw_kernel<<<grid, 256, 0, st>>>(X, V, B, H, W, C, nH, nW, relu, scale, shift);
         }
