@@ -142,6 +142,31 @@ class ResNet18Var(torch.nn.Module):
         l = torch.relu(l).mean(dim=(2, 3))
         return F.linear(l, self.fc_w, self.fc_b)
 
+    def winograd_layers(self):
+        """name -> layer, with the reference's variable names 'Winograd_W<stage><block>_<2a|2b>/W'."""
+        out = {}
+        for s, (blk_a, blk_b) in enumerate(self.blocks):
+            for tag, blk in (("a", blk_a), ("b", blk_b)):
+                for conv in ("2a", "2b"):
+                    out["Winograd_W%d%s_%s/W" % (s + 2, tag, conv)] = blk["w" + conv]
+        return out
+
+    def load_winograd_weights(self, weights, masks=None):
+        """Install (16,C,K) weights (and masks) from dicts keyed like the reference checkpoint / mask pickle
+        (see wg_weights.load_npz, wg_weights.load_mask_pickle).  Missing names keep their random values."""
+        for name, layer in self.winograd_layers().items():
+            if name not in weights:
+                continue
+            w = torch.as_tensor(np.asarray(weights[name]), dtype=torch.float32, device=layer.W.device)
+            if tuple(w.shape) != tuple(layer.W.shape):
+                raise ValueError("%s: expected %s, got %s" % (name, tuple(layer.W.shape), tuple(w.shape)))
+            if masks is not None and name in masks:
+                m = torch.as_tensor(np.asarray(masks[name]), dtype=torch.float32, device=layer.W.device)
+                layer.mask.copy_(m)
+                w = w * m
+            layer.W.copy_(w)
+            layer._prepared = None
+
     def winograd_flops(self, batch, size=224):
         """Dense Winograd-domain flops 2*16*P*C*K summed over the 16 layers (independent of the masks)."""
         sp = size // 4

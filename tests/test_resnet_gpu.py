@@ -26,3 +26,21 @@ def test_winograd_flops_count():
     m = ResNet18Var(stage5_pool=True)
     assert abs(m.winograd_flops(1) / 1e6 - 1600.2) < 1.0      # MFLOP per image, stage 5 at 7x7
     assert abs(ResNet18Var(stage5_pool=False).winograd_flops(1) / 1e6 - 2569.0) < 1.5   # at 14x14, as the reference runs it
+
+
+def test_load_weights_and_masks_by_reference_names():
+    import numpy as np
+    import wg_weights as ww
+    from resnet18_var import ResNet18Var
+    model = ResNet18Var(seed=1).cuda().eval()
+    layers = model.winograd_layers()
+    assert tuple(sorted(layers)) == tuple(sorted(ww.RESNET18_LAYER_NAMES))
+    rng = np.random.default_rng(0)
+    weights = {n: rng.standard_normal(tuple(l.W.shape)).astype(np.float32) for n, l in layers.items()}
+    pruned, masks = ww.prune_layers(weights, 0.3)
+    model.load_winograd_weights(weights, masks)
+    for n, l in layers.items():
+        assert np.array_equal(l.W.cpu().numpy(), pruned[n]) and abs(float(l.mask.mean()) - 0.3) < 1e-3
+    x = torch.randn((1, 3, 64, 64), device="cuda")
+    with torch.no_grad():
+        assert torch.isfinite(model(x)).all()
