@@ -157,6 +157,23 @@ int wg2x2_layer_fwd(const float *X, const float *Wt, float *Y, float *V_out, int
 size_t wg2x2_layer_fwd_workspace_bytes(int B, int H, int W, int C, int K, int math, int keep_V);
 
 /*
+ * Whole layer forward with prepared weights (tensor-core path), the call pair of
+ * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119 in its fastest form for the shape:
+ *  - one kernel (wg2x2_layer_fwd_fused) where that is supported (NCHW, W % 4 == 0, C % 16 == 0) and either
+ *    C <= 64 or no V_scratch was given: transform and ReLU happen on the SM, the transformed input is never
+ *    written to memory;
+ *  - otherwise the two kernels with V_scratch (16*B*nH*nW*C floats) in between; WG2X2_ERR_WORKSPACE if NULL.
+ * out_scale/out_shift/residual as in wg2x2_conv_fwd_prepared_fused (each may be NULL).
+ */
+int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, float *V_scratch, int B, int H, int W,
+                             int C, int K, int layout, int relu, const float *out_scale, const float *out_shift,
+                             const float *residual, void *stream);
+int wg2x2_layer_fwd_fused_supported(int B, int H, int W, int C, int K, int layout);
+/* The one-kernel layer forward on its own (NCHW in and out); WG2X2_ERR_UNSUPPORTED outside the shapes above. */
+int wg2x2_layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
+                          const float *out_scale, const float *out_shift, const float *residual, void *stream);
+
+/*
  * Status word of the most recent kernel on this device that uses bounded waits
  * (the tcgen05 path): 0, or WG2X2_ERR_TIMEOUT with a code saying where it gave up.
  * Synchronises the given stream.

@@ -25,6 +25,9 @@ size_t prepared_weights_bytes(int C, int K);
 int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
                          int layout, const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
+bool fused_fwd_supported(int B, int H, int W, int C, int K, int layout);
+int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
+                    const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
 size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW);
 int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *mask, float *dV, float *dW, int B, int H, int W,
                 int C, int K, int layout, int relu, void *ws, size_t ws_bytes, cudaStream_t st);
@@ -171,6 +174,36 @@ int wg2x2_layer_fwd(const float *X, const float *Wt, float *Y, float *V_out, int
     int s = wg2x2_imtrans_fwd(X, Vbuf, B, H, W, C, layout, relu, stream);
     if (s != WG2X2_OK) return s;
     return wg2x2_conv_fwd(Vbuf, Wt, Y, B, nH, nW, C, K, H, W, layout, math, workspace, conv_ws, stream);
+}
+
+int wg2x2_layer_fwd_fused_supported(int B, int H, int W, int C, int K, int layout)
+{
+    return (B > 0 && H > 0 && W > 0 && C > 0 && K > 0 && fused_fwd_supported(B, H, W, C, K, layout)) ? 1 : 0;
+}
+
+int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, float *V_scratch, int B, int H, int W, int C, int K,
+                             int layout, int relu, const float *out_scale, const float *out_shift, const float *residual,
+                             void *stream)
+{
+    if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!layout_ok(layout)) return WG2X2_ERR_BAD_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // The one-kernel path wins where the product is cheap next to the V round trip (few channels); with more
+    // channels its on-SM transform, bound by instruction issue, is slower than the two HBM-bound kernels.
+    if (fused_fwd_supported(B, H, W, C, K, layout) && (C <= 64 || !V_scratch))
+        return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, out_scale, out_shift, residual, st);
+    if (!V_scratch) return WG2X2_ERR_WORKSPACE;
+    const int nH = (H + 1) / 2, nW = (W + 1) / 2;
+    const int s = imtrans_fwd(X, V_scratch, B, H, W, C, layout, relu, nullptr, nullptr, st);
+    if (s != WG2X2_OK) return s;
+    return conv_fwd_tc_prepared(V_scratch, prepared, Y, B, nH, nW, C, K, H, W, layout, out_scale, out_shift, residual, st);
+}
+
+int wg2x2_layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
+                          const float *out_scale, const float *out_shift, const float *residual, void *stream)
+{
+    if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, out_scale, out_shift, residual, (cudaStream_t)stream);
 }
 
 int wg2x2_last_device_status(void *stream, unsigned int *where)

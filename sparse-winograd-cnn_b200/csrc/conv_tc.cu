@@ -651,6 +651,7 @@ int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW
 void dw_reduce_launch(const float *partial, const float *mask, float *dW, long long n, int splits, cudaStream_t st);  // conv_ffma.cu
 
 #include "conv_tc_bwd.cuh"
+#include "conv_tc_fused.cuh"
 
 #ifdef WG_TC_TRACE
 extern "C" int wg2x2_debug_read_trace(long long *host, int n)

@@ -47,6 +47,9 @@ _SIGS = {
     "wg2x2_conv_bwd_dw_noalloc_max_bytes": (_z, []),
     "wg2x2_layer_fwd": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_layer_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
+    "wg2x2_layer_fwd_prepared": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "wg2x2_layer_fwd_fused": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "wg2x2_layer_fwd_fused_supported": (_i, [_i, _i, _i, _i, _i, _i]),
     "wg2x2_last_device_status": (_i, [_p, ctypes.POINTER(ctypes.c_uint)]),
 }
 for _name, (_res, _args) in _SIGS.items():

@@ -166,6 +166,38 @@ def layer_fwd(x, Wt, relu=True, layout="NHWC", math="fp32", keep_V=False, out=No
     return (Y, V) if keep_V else Y
 
 
+def fused_supported(B, H, W, C, K, layout="NCHW"):
+    return bool(lib.wg2x2_layer_fwd_fused_supported(B, H, W, C, K, _LAYOUTS[layout]))
+
+
+def layer_fwd_prepared(x, prepared, K, relu=True, layout="NHWC", out=None, V_scratch=None, out_scale=None, out_shift=None,
+                       residual=None):
+    """Whole layer with prepared weights: one fused kernel where supported (V never stored), else transform +
+    product through V_scratch (allocated here when not given)."""
+    layout = _LAYOUTS[layout]
+    _chk(x, "x")
+    B, H, W, C = _img_dims(x, layout)
+    Y = out if out is not None else torch.empty(_img_shape(B, H, W, K, layout), dtype=torch.float32, device=x.device)
+    if V_scratch is None and not lib.wg2x2_layer_fwd_fused_supported(B, H, W, C, K, layout):
+        V_scratch = torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_layer_fwd_prepared(_ptr(x), _ptr(prepared), _ptr(Y), _ptr(V_scratch), B, H, W, C, K, layout,
+                                                int(bool(relu)), _ptr(out_scale), _ptr(out_shift), _ptr(residual), _stream()),
+                   "wg2x2_layer_fwd_prepared")
+    return Y
+
+
+def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shift=None, residual=None):
+    """The one-kernel layer forward (NCHW); raises Wg2x2Error(UNSUPPORTED) for other shapes."""
+    _chk(x, "x")
+    B, C, H, W = x.shape
+    Y = out if out is not None else torch.empty((B, K, H, W), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_layer_fwd_fused(_ptr(x), _ptr(prepared), _ptr(Y), B, H, W, C, K, int(bool(relu)), _ptr(out_scale),
+                                             _ptr(out_shift), _ptr(residual), _stream()), "wg2x2_layer_fwd_fused")
+    return Y
+
+
 def last_device_status():
     import ctypes
     where = ctypes.c_uint(0)

@@ -178,3 +178,47 @@ def test_fused_affine_and_residual(wg, oracle, shape, layout):
     got2 = Y2 if layout == "NHWC" else np.transpose(Y2, (0, 2, 3, 1))
     assert oracle.max_rel(got2, oracle.conv_fwd(Vo, Wt, H, W) + R) <= TOL_TF32
     _status_ok(wg)
+
+
+FUSED_SHAPES = [  # B, H, W, C, K  (NCHW, W % 4 == 0, C % 16 == 0)
+    (2, 56, 56, 64, 64), (3, 28, 28, 128, 128), (5, 8, 8, 32, 64), (2, 12, 16, 16, 24), (9, 4, 4, 64, 96),
+    (1, 56, 72, 32, 32), (2, 7, 8, 48, 64),
+]
+
+
+@pytest.mark.parametrize("shape", FUSED_SHAPES)
+def test_fused_layer_forward(wg, oracle, shape):
+    """One-kernel layer forward (V never stored) against the float64 oracle, with and without the epilogue extras."""
+    B, H, W, C, K = shape
+    assert wg.fused_supported(B, H, W, C, K, "NCHW")
+    X, Wt = _inputs(shape)
+    xl = np.ascontiguousarray(np.transpose(X, (0, 3, 1, 2)))
+    prepared = wg.prepare_weights(_dev(Wt))
+    want = oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)
+    Y = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=True)
+    _status_ok(wg)
+    got = np.transpose(Y.cpu().numpy(), (0, 2, 3, 1))
+    Yauto = wg.layer_fwd_prepared(_dev(xl), prepared, K, relu=True, layout="NCHW")   # picks a path by shape
+    assert oracle.max_rel(np.transpose(Yauto.cpu().numpy(), (0, 2, 3, 1)), want) <= TOL_TF32
+    assert np.isfinite(got).all()
+    err = oracle.max_rel(got, want)
+    assert err <= TOL_TF32, "max_rel %.3g" % err
+    # no ReLU, plus affine output and residual
+    rng = np.random.default_rng(3)
+    s_out, b_out = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32), (0.3 * rng.standard_normal(K)).astype(np.float32)
+    R = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    Y2 = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=False, out_scale=_dev(s_out), out_shift=_dev(b_out),
+                            residual=_dev(np.ascontiguousarray(np.transpose(R, (0, 3, 1, 2)))))
+    want2 = oracle.conv_fwd(oracle.imtrans_fwd(X, relu=False), Wt, H, W) * s_out + b_out + R
+    assert oracle.max_rel(np.transpose(Y2.cpu().numpy(), (0, 2, 3, 1)), want2) <= TOL_TF32
+    _status_ok(wg)
+
+
+def test_layer_fwd_prepared_falls_back_to_two_kernels(wg, oracle):
+    shape = (2, 7, 7, 36, 20)        # odd width: not a fused shape
+    B, H, W, C, K = shape
+    assert not wg.fused_supported(B, H, W, C, K, "NCHW")
+    X, Wt = _inputs(shape)
+    prepared = wg.prepare_weights(_dev(Wt))
+    Y = wg.layer_fwd_prepared(_dev(X), prepared, K, relu=True, layout="NHWC")
+    assert oracle.max_rel(Y.cpu().numpy(), oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)) <= TOL_TF32
