@@ -363,9 +363,12 @@ def main():
     # the weights do not change between forward passes: the tensor-core path repacks them once
     prepared = wg2x2.prepare_weights(Wt) if args.math == "tf32" else None
 
+    cws_n = wg2x2._lib.lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, nH, nW, C, K) if prepared is not None else 0
+    cws = torch.empty(cws_n, dtype=torch.uint8, device=dev) if cws_n else None   # products of the wide path (C, K >= 256)
+
     def conv(i):
         if prepared is not None:
-            wg2x2.conv_fwd_prepared(V, prepared, K, H, W, layout=args.layout, out=Y)
+            wg2x2.conv_fwd_prepared(V, prepared, K, H, W, layout=args.layout, out=Y, workspace=cws)
         else:
             wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
 

@@ -112,6 +112,18 @@ int wg2x2_conv_fwd_prepared_fused(const float *V, const void *prepared, float *Y
                                   const float *residual, void *stream);
 
 /*
+ * wg2x2_conv_fwd_prepared_fused with scratch memory, which lets layers with many channels (C, K >= 256) take
+ * the wide path: the 16 products as GEMMs with 256 output channels per unit into `workspace` (16*P*K floats,
+ * wg2x2_conv_fwd_prepared_workspace_bytes; 0 = the shape does not use it), then one pass for A^T m A — the
+ * reference's own two-step structure (winograd2x2_conv_cuda.cu.cc:80-89) on tensor cores.  With workspace ==
+ * NULL, or for smaller layers, the single-kernel path of wg2x2_conv_fwd_prepared_fused runs.
+ */
+int wg2x2_conv_fwd_prepared_ws(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K,
+                               int out_h, int out_w, int layout, const float *out_scale, const float *out_shift,
+                               const float *residual, void *workspace, size_t workspace_bytes, void *stream);
+size_t wg2x2_conv_fwd_prepared_workspace_bytes(int B, int nH, int nW, int C, int K);
+
+/*
  * Gradient of the product/output-transform op for dY of size (B,H,W,K):
  *   dV_t = (A dY A^T)_t . W_t^T   (skipped when dV == NULL)
  *   dW_t = V_t^T . (A dY A^T)_t   (skipped when dW == NULL), multiplied by mask when mask != NULL

@@ -25,6 +25,11 @@ size_t prepared_weights_bytes(int C, int K);
 int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
                          int layout, const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
+bool conv_fwd_wide_preferred(int C, int K);
+size_t conv_fwd_wide_workspace_bytes(long long P, int K);
+int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
+                     int layout, const float *out_scale, const float *out_shift, const float *residual, void *ws, size_t ws_bytes,
+                     cudaStream_t st);
 bool fused_fwd_supported(int B, int H, int W, int C, int K, int layout);
 int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
                     const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
@@ -174,6 +179,26 @@ int wg2x2_layer_fwd(const float *X, const float *Wt, float *Y, float *V_out, int
     int s = wg2x2_imtrans_fwd(X, Vbuf, B, H, W, C, layout, relu, stream);
     if (s != WG2X2_OK) return s;
     return wg2x2_conv_fwd(Vbuf, Wt, Y, B, nH, nW, C, K, H, W, layout, math, workspace, conv_ws, stream);
+}
+
+size_t wg2x2_conv_fwd_prepared_workspace_bytes(int B, int nH, int nW, int C, int K)
+{
+    if (B <= 0 || nH <= 0 || nW <= 0 || C <= 0 || K <= 0 || !conv_fwd_wide_preferred(C, K)) return 0;
+    return conv_fwd_wide_workspace_bytes((long long)B * nH * nW, K);
+}
+
+int wg2x2_conv_fwd_prepared_ws(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int out_h,
+                               int out_w, int layout, const float *out_scale, const float *out_shift, const float *residual,
+                               void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!V || !prepared || !Y || B <= 0 || nH <= 0 || nW <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!layout_ok(layout) || !crop_ok(out_h, nH) || !crop_ok(out_w, nW)) return WG2X2_ERR_BAD_ARG;
+    if ((out_scale == nullptr) != (out_shift == nullptr)) return WG2X2_ERR_BAD_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (conv_fwd_wide_preferred(C, K) && workspace)
+        return conv_fwd_tc_wide(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, out_scale, out_shift, residual, workspace,
+                                workspace_bytes, st);
+    return conv_fwd_tc_prepared(V, prepared, Y, B, nH, nW, C, K, out_h, out_w, layout, out_scale, out_shift, residual, st);
 }
 
 int wg2x2_layer_fwd_fused_supported(int B, int H, int W, int C, int K, int layout)

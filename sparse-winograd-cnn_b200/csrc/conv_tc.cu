@@ -631,11 +631,18 @@ int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, 
                      out_scale, out_shift, residual, st);
 }
 
+bool conv_fwd_wide_preferred(int C, int K);
+size_t conv_fwd_wide_workspace_bytes(long long P, int K);
+int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
+                     int layout, const float *out_scale, const float *out_shift, const float *residual, void *ws, size_t ws_bytes,
+                     cudaStream_t st);
+
 size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K)
 {
-    (void)B; (void)nH; (void)nW;
-    if (C <= 0 || K <= 0) return 0;
-    return prepared_weights_bytes(C, K);
+    if (C <= 0 || K <= 0 || B <= 0 || nH <= 0 || nW <= 0) return 0;
+    size_t n = prepared_weights_bytes(C, K);
+    if (conv_fwd_wide_preferred(C, K)) n += conv_fwd_wide_workspace_bytes((long long)B * nH * nW, K);
+    return n;
 }
 
 int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW, int layout,
@@ -645,6 +652,10 @@ int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW
     if (!ws || ws_bytes < prepared_weights_bytes(C, K)) return WG2X2_ERR_WORKSPACE;
     const int s = weights_prepare(Wt, C, K, ws, ws_bytes, st);
     if (s != WG2X2_OK) return s;
+    const size_t pb = prepared_weights_bytes(C, K);
+    if (conv_fwd_wide_preferred(C, K) && ws_bytes >= pb + conv_fwd_wide_workspace_bytes((long long)B * nH * nW, K))
+        return conv_fwd_tc_wide(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, nullptr, nullptr, nullptr,
+                                static_cast<char *>(ws) + pb, ws_bytes - pb, st);
     return conv_fwd_tc_prepared(V, ws, Y, B, nH, nW, C, K, outH, outW, layout, nullptr, nullptr, nullptr, st);
 }
 

@@ -508,3 +508,151 @@ int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *m
     }
     return WG2X2_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Wide forward path for layers with many channels (C, K >= 256): the 16 products as plain GEMMs with
+// N = 256 output channels per unit (conv_grad_gemm_tc_kernel<1>: same operands' major-ness as dV), the
+// products M (16, P, K) written once to scratch memory, then one HBM-bound pass for A^T m A.  With N = 64
+// (the row-walk kernel, which needs four accumulators live per unit) every A tile is re-read from L2 and
+// from shared memory four times as often, and that, not HBM, is what bounds these shapes.
+// ---------------------------------------------------------------------------------------
+struct OutExtras {
+    const float *scale, *shift, *residual;
+};
+
+// NHWC: one thread = one tile x 4 output channels
+__global__ void __launch_bounds__(256) out_transform_nhwc_kernel(const float *__restrict__ M, float *__restrict__ Y, long long P,
+                                                                   int nH, int nW, int K, int outH, int outW, OutExtras ex)
+{
+    const int KV = K >> 2;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= P * KV) return;
+    const int kv = (int)(idx % KV);
+    const long long p = idx / KV;
+    const int tw = (int)(p % nW), th = (int)((p / nW) % nH), b = (int)(p / ((long long)nW * nH));
+    float4 y[2][2];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) y[a][e] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float4 m[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[j] = __ldg(reinterpret_cast<const float4 *>(M + ((long long)(4 * i + j) * P + p) * K) + kv);
+        const float4 z0 = make_float4(m[0].x + m[1].x + m[2].x, m[0].y + m[1].y + m[2].y, m[0].z + m[1].z + m[2].z, m[0].w + m[1].w + m[2].w);
+        const float4 z1 = make_float4(m[1].x - m[2].x - m[3].x, m[1].y - m[2].y - m[3].y, m[1].z - m[2].z - m[3].z, m[1].w - m[2].w - m[3].w);
+        if (i <= 2) { y[0][0] = y[0][0] + z0; y[0][1] = y[0][1] + z1; }
+        if (i == 1) { y[1][0] = y[1][0] + z0; y[1][1] = y[1][1] + z1; }
+        if (i >= 2) { y[1][0] = y[1][0] - z0; y[1][1] = y[1][1] - z1; }
+    }
+    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ex.scale) { sc = __ldg(reinterpret_cast<const float4 *>(ex.scale) + kv); sh = __ldg(reinterpret_cast<const float4 *>(ex.shift) + kv); }
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int h = 2 * th + a, w = 2 * tw + e;
+            if (h >= outH || w >= outW) continue;
+            const long long o = ((((long long)b * outH + h) * outW + w) * K) / 4 + kv;
+            float4 v = y[a][e];
+            if (ex.scale) { v.x = fmaf(v.x, sc.x, sh.x); v.y = fmaf(v.y, sc.y, sh.y); v.z = fmaf(v.z, sc.z, sh.z); v.w = fmaf(v.w, sc.w, sh.w); }
+            if (ex.residual) { const float4 r = __ldg(reinterpret_cast<const float4 *>(ex.residual) + o); v = v + r; }
+            reinterpret_cast<float4 *>(Y)[o] = v;
+        }
+}
+
+// NCHW: lane = output channel over a band of R tile rows; the 2R x outW pixels of each channel collect in
+// shared memory and leave as one contiguous run per channel.
+__global__ void __launch_bounds__(256) out_transform_nchw_kernel(const float *__restrict__ M, float *__restrict__ Y, long long P,
+                                                                   int nH, int nW, int K, int outH, int outW, int R, int nbands,
+                                                                   int pitch, OutExtras ex)
+{
+    extern __shared__ float O[];
+    const int band = blockIdx.x % nbands;
+    const int b = blockIdx.x / nbands;
+    const int k0 = blockIdx.y * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int th0 = band * R;
+    const int rows_blk = min(R, nH - th0);
+    const bool k_ok = k0 + lane < K;
+    const float sc = (ex.scale && k_ok) ? __ldg(ex.scale + k0 + lane) : 1.f;
+    const float sh = (ex.scale && k_ok) ? __ldg(ex.shift + k0 + lane) : 0.f;
+    for (int q = warp; q < rows_blk * nW; q += 8) {
+        const int br = q / nW, tw = q - br * nW;
+        const long long p = ((long long)b * nH + th0 + br) * nW + tw;
+        float y[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        if (k_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float m[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) m[j] = __ldg(M + ((long long)(4 * i + j) * P + p) * K + k0 + lane);
+                float z0, z1;
+                at_cols(m[0], m[1], m[2], m[3], z0, z1);
+                at_rows_accum(i, z0, z1, y);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+                if (2 * tw + e < outW) O[lane * pitch + (2 * br + a) * outW + 2 * tw + e] = fmaf(y[a][e], sc, sh);
+    }
+    __syncthreads();
+    const int lo = 2 * th0, hi = min(2 * th0 + 2 * rows_blk, outH);
+    const int n = (hi - lo) * outW;
+    for (int kk = warp; kk < 32; kk += 8) {
+        if (k0 + kk >= K) break;
+        const long long o = (((long long)b * K + k0 + kk) * outH + lo) * outW;
+        const float *src = O + kk * pitch;
+        if (ex.residual) { for (int i = lane; i < n; i += 32) Y[o + i] = src[i] + __ldg(ex.residual + o + i); }
+        else             { for (int i = lane; i < n; i += 32) Y[o + i] = src[i]; }
+    }
+}
+
+bool conv_fwd_wide_preferred(int C, int K) { return C >= 256 && K >= 256 && C % 4 == 0 && K % 4 == 0; }
+size_t conv_fwd_wide_workspace_bytes(long long P, int K) { return align_up((size_t)16 * P * K * sizeof(float), 256); }
+
+int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
+                     int layout, const float *out_scale, const float *out_shift, const float *residual, void *ws, size_t ws_bytes,
+                     cudaStream_t st)
+{
+    const long long P = (long long)B * nH * nW;
+    if (P > 0x7fffffffLL - 128) return WG2X2_ERR_UNSUPPORTED;
+    if (!ws || ws_bytes < conv_fwd_wide_workspace_bytes(P, K) || (reinterpret_cast<uintptr_t>(ws) & 255u)) return WG2X2_ERR_WORKSPACE;
+    float *M = static_cast<float *>(ws);
+    GgParams prm;
+    prm.rows = P; prm.cols = K; prm.contr = C;
+    prm.N = gg_cols(K);
+    prm.nRB = (int)cdivll(P, 128);
+    prm.nCB = cdiv(K, prm.N);
+    prm.splits = 1;
+    prm.chunks_per_split = cdiv(C, 32);
+    prm.units = 16 * prm.nRB * prm.nCB;
+    prm.direct = 1;
+    prm.out = M;
+    prm.mask = nullptr;
+    CUtensorMap mapA, mapB;
+    if (!make_map_gg(&mapA, V, C, P, false, 128) || !make_map_gg(&mapB, static_cast<const float *>(prepared), C, K, false, prm.N))
+        return WG2X2_ERR_LAUNCH;
+    int s = gg_launch<1>(mapA, mapB, prm, st);
+    if (s != WG2X2_OK) return s;
+    OutExtras ex{out_scale, out_shift, residual};
+    if (layout == WG2X2_NHWC) {
+        out_transform_nhwc_kernel<<<(unsigned)cdivll(P * (K / 4), 256), 256, 0, st>>>(M, Y, P, nH, nW, K, outH, outW, ex);
+    } else {
+        int R = 384 / (2 * outW);
+        if (R < 1) R = 1;
+        if (R > nH) R = nH;
+        const int nbands = cdiv(nH, R);
+        const int pitch = (2 * R * outW) | 1;
+        const int smem = 32 * pitch * (int)sizeof(float);
+        if ((long long)B * nbands > 0x7fffffffLL || smem > 200 * 1024) return WG2X2_ERR_UNSUPPORTED;
+        if (cudaFuncSetAttribute(out_transform_nchw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return WG2X2_ERR_LAUNCH;
+        out_transform_nchw_kernel<<<dim3((unsigned)(B * nbands), cdiv(K, 32)), 256, smem, st>>>(M, Y, P, nH, nW, K, outH, outW, R,
+                                                                                                 nbands, pitch, ex);
+    }
+    return launch_status();
+}

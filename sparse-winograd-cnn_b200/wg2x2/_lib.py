@@ -41,6 +41,8 @@ _SIGS = {
     "wg2x2_weights_prepare": (_i, [_p, _i, _i, _p, _z, _p]),
     "wg2x2_conv_fwd_prepared": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p]),
     "wg2x2_conv_fwd_prepared_fused": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "wg2x2_conv_fwd_prepared_ws": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _z, _p]),
+    "wg2x2_conv_fwd_prepared_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
     "wg2x2_conv_bwd": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_conv_bwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_conv_bwd_dw_noalloc": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p]),

@@ -102,7 +102,7 @@ def prepare_weights(Wt):
 
 
 def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out=None, out_scale=None, out_shift=None,
-                      residual=None):
+                      residual=None, workspace=None, wide=True):
     """As conv_fwd(math="tf32") with weights already prepared by prepare_weights; optionally
     Y = acc*out_scale[k] + out_shift[k] + residual in the kernel's epilogue."""
     layout = _LAYOUTS[layout]
@@ -111,6 +111,16 @@ def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out
     out_h = 2 * nH if out_h is None else out_h
     out_w = 2 * nW if out_w is None else out_w
     Y = out if out is not None else torch.empty(_img_shape(B, out_h, out_w, K, layout), dtype=torch.float32, device=V.device)
+    nws = lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, nH, nW, C, K) if wide else 0
+    if nws:   # many channels: products as wide GEMMs into scratch memory, then the output transform
+        if residual is not None:
+            _chk(residual, "residual")
+        ws = workspace if workspace is not None and workspace.numel() >= nws else torch.empty(nws, dtype=torch.uint8, device=V.device)
+        with torch.cuda.device(V.device):
+            _lib.check(lib.wg2x2_conv_fwd_prepared_ws(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
+                                                      _ptr(out_scale), _ptr(out_shift), _ptr(residual), _ptr(ws), ws.numel(),
+                                                      _stream()), "wg2x2_conv_fwd_prepared_ws")
+        return Y
     with torch.cuda.device(V.device):
         if out_scale is None and residual is None:
             _lib.check(lib.wg2x2_conv_fwd_prepared(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,

@@ -89,7 +89,7 @@ def test_pruned_weights_and_block_skipping(wg, oracle):
     blocks[:, 0, :] |= rng.random((16, K // 64)) < 0.5    # some first chunks empty as well
     Wb = Wt * np.repeat(np.repeat(blocks, 32, axis=1), 64, axis=2)
     prepared = wg.prepare_weights(_dev(Wb))
-    Yb = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W).cpu().numpy()
+    Yb = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, wide=False).cpu().numpy()   # the row-walk kernel, which skips blocks
     _status_ok(wg)
     assert oracle.max_rel(Yb, oracle.conv_fwd(V, Wb, H, W)) <= TOL_TF32
     # all-zero weights: the output must be exactly zero, not stale accumulator contents
@@ -222,3 +222,31 @@ def test_layer_fwd_prepared_falls_back_to_two_kernels(wg, oracle):
     prepared = wg.prepare_weights(_dev(Wt))
     Y = wg.layer_fwd_prepared(_dev(X), prepared, K, relu=True, layout="NHWC")
     assert oracle.max_rel(Y.cpu().numpy(), oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+@pytest.mark.parametrize("shape", [(3, 14, 14, 256, 256), (16, 7, 7, 512, 512), (2, 9, 13, 260, 264), (1, 28, 28, 256, 320)])
+def test_wide_forward_path(wg, oracle, shape, layout):
+    """Layers with many channels: products as wide GEMMs into scratch memory + output transform pass, against the
+    oracle and against the single-kernel path; with the epilogue extras too."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    want = oracle.conv_fwd(V, Wt, H, W)
+    prepared = wg.prepare_weights(_dev(Wt))
+    fix = (lambda a: a) if layout == "NHWC" else (lambda a: np.transpose(a, (0, 2, 3, 1)))
+    to_l = (lambda a: a) if layout == "NHWC" else (lambda a: np.ascontiguousarray(np.transpose(a, (0, 3, 1, 2))))
+    assert wg._lib.lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, (H + 1) // 2, (W + 1) // 2, C, K) > 0
+    Yw = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, layout=layout).cpu().numpy()
+    Yn = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, layout=layout, wide=False).cpu().numpy()
+    assert oracle.max_rel(fix(Yw), want) <= TOL_TF32 and oracle.max_rel(fix(Yn), want) <= TOL_TF32
+    assert oracle.max_rel(Yw, Yn) <= 1e-5          # same TF32 products, fp32 sums in a different order
+    rng = np.random.default_rng(8)
+    s_out, b_out = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32), (0.3 * rng.standard_normal(K)).astype(np.float32)
+    R = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    Ye = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, layout=layout, out_scale=_dev(s_out), out_shift=_dev(b_out),
+                              residual=_dev(to_l(R))).cpu().numpy()
+    assert oracle.max_rel(fix(Ye), want * s_out + b_out + R) <= TOL_TF32
+    Yc = wg.conv_fwd(_dev(V), _dev(Wt), H, W, layout=layout, math="tf32").cpu().numpy()      # raw-weight entry point
+    assert oracle.max_rel(fix(Yc), want) <= TOL_TF32
+    _status_ok(wg)
