@@ -30,6 +30,8 @@ class HostLayerPipeline:
             self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
             self.ev_in = [torch.cuda.Event() for _ in self.bounds]
             self.ev_run = [torch.cuda.Event() for _ in self.bounds]
+            self.ev_out = [torch.cuda.Event() for _ in self.bounds]
+        self._used = False
         self._prepared, self._prepared_for = None, None
 
     def _weights(self, Wt):
@@ -41,20 +43,28 @@ class HostLayerPipeline:
             self._prepared_for = key
         return self._prepared
 
-    def __call__(self, x_host, Wt, y_host):
-        """x_host, y_host: pinned host tensors of the full batch; returns y_host (complete on return of
-        `torch.cuda.current_stream().synchronize()` -- the caller's stream waits for the last copy)."""
+    def submit(self, x_host, Wt, y_host):
+        """Enqueue one batch (pinned host x_host -> pinned host y_host) and return the CUDA event that marks its
+        last device-to-host copy.  Calls may follow one another without waiting: the copies of the next batch
+        overlap the kernels and the read-back of this one, so that in steady state the PCIe link is busy in both
+        directions all the time.  Device buffers are reused across calls; the event dependencies below keep a
+        chunk's buffers from being overwritten while the previous batch still uses them.  The caller must not
+        reuse y_host (or change x_host) before the returned event has completed."""
         cur = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_run, self.s_out):
-            s.wait_stream(cur)
+        self.s_in.wait_stream(cur)
+        self.s_run.wait_stream(cur)
         with torch.cuda.stream(self.s_run):
             prepared = self._weights(Wt)
         for i, (lo, hi) in enumerate(self.bounds):
             with torch.cuda.stream(self.s_in):
+                if self._used:
+                    self.s_in.wait_event(self.ev_run[i])      # the previous batch's kernels have read xd[i]
                 self.xd[i].copy_(x_host[lo:hi], non_blocking=True)
                 self.ev_in[i].record()
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(self.ev_in[i])
+                if self._used:
+                    self.s_run.wait_event(self.ev_out[i])     # the previous batch's yd[i] has been copied out
                 shape = self.vshape(hi - lo)
                 v = self.vflat[i % 2][:shape[0] * shape[1] * shape[2] * shape[3] * shape[4]].view(shape)
                 ops.imtrans_fwd(self.xd[i], relu=self.relu, layout=self.layout, out=v)
@@ -66,7 +76,15 @@ class HostLayerPipeline:
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_run[i])
                 y_host[lo:hi].copy_(self.yd[i], non_blocking=True)
-        cur.wait_stream(self.s_out)
-        cur.wait_stream(self.s_in)
-        cur.wait_stream(self.s_run)
+                self.ev_out[i].record()
+        self._used = True
+        done = torch.cuda.Event()
+        done.record(self.s_out)
+        return done
+
+    def __call__(self, x_host, Wt, y_host):
+        """x_host, y_host: pinned host tensors of the full batch.  Returns y_host; it is complete once the
+        caller's current stream has run past this call (e.g. after torch.cuda.current_stream().synchronize())."""
+        done = self.submit(x_host, Wt, y_host)
+        torch.cuda.current_stream(self.device).wait_event(done)
         return y_host

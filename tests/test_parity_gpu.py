@@ -319,3 +319,11 @@ def test_host_pipeline_equals_resident_call(wg, oracle, layout):
         assert torch.equal(yh, want.cpu())
     _check(_from_layout(yh, layout), oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W), tol=5e-3, tol_l1=5e-3,
            what="pipeline vs oracle")
+    # back-to-back submissions with different inputs and two output buffers: every result must be its own batch's
+    xs = [xh, (xh * 0.5 + 1.0).pin_memory(), (xh * -1.0).pin_memory()]
+    ys = [torch.empty_like(yh).pin_memory() for _ in xs]
+    evs = [pipe.submit(xi, wt, yi) for xi, yi in zip(xs, ys)]
+    for e in evs:
+        e.synchronize()
+    for xi, yi in zip(xs, ys):
+        assert torch.equal(yi, wg.layer_fwd(xi.cuda(), wt, relu=True, layout=layout, math="tf32").cpu())
