@@ -148,7 +148,7 @@ def run_reference(args, wl, rank, world):
 
 
 def run_backward(args, rank, world, local):
-    """BASELINE config 5: backward of a pruned conv5_x-shaped layer (N=256, C=K=512, 7x7, density 0.2):
+    """Backward workload (cfg5): backward of a pruned conv5_x-shaped layer (N=256, C=K=512, 7x7, density 0.2):
     dX through the transposed products plus the input-transform gradient (ReLU mask applied), and the
     masked dW.  Per-GPU batch fixed (weak scaling); dW would need one all-reduce when sharded, which is
     reported separately and not part of the step."""
@@ -215,7 +215,7 @@ def run_backward(args, rank, world, local):
 
 
 def run_resnet(args, rank, world, local):
-    """BASELINE config 4: ResNet-18-var forward, batch 256 in total, sharded over the ranks (strong scaling)."""
+    """Network workload (cfg4): ResNet-18-var forward, batch 256 in total, sharded over the ranks (strong scaling)."""
     import torch
     import torch.distributed as dist
     import wg2x2  # noqa: F401

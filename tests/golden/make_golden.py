@@ -8,7 +8,7 @@ winograd2x2_imTrans_grad_test.py:158-161, winograd2x2_conv_grad_test.py:160-163)
 larger even-sized ones.  Only even image sizes: the upstream gradient kernels read out of
 bounds for odd ones.
 
-    python tests/golden/make_golden.py [outdir]      (default: gpurun_out/golden)
+    python tests/golden/make_golden.py [outdir]      (default: tests/golden/_new)
 """
 import ctypes
 import os
@@ -28,7 +28,7 @@ CASES = [  # name, B, H, W, C, K
 
 
 def main():
-    out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "tests", "golden", "_new")
     os.makedirs(out, exist_ok=True)
     ref = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libwg_ref_cuda.so"))
     dev = torch.device("cuda:0")

@@ -3,7 +3,7 @@
 The function is taken as text from ResNet-18-var/prune_script.py (the module itself imports TensorFlow
 and cannot be imported here), executed on seeded inputs, and its masks and pruned arrays stored.
 
-    python tests/golden/make_prune_golden.py /root/reference
+    python tests/golden/make_prune_golden.py <reference checkout>
 """
 import ast
 import os

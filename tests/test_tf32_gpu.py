@@ -10,7 +10,7 @@ TOL_TF32 = 5e-3
 
 SHAPES = [  # B, H, W, C, K
     (2, 14, 14, 64, 64),      # one partial m-tile
-    (4, 56, 56, 64, 64),      # BASELINE config 1
+    (4, 56, 56, 64, 64),      # the small 56x56 layer
     (3, 6, 6, 32, 32), (3, 6, 6, 32, 64),
     (2, 7, 7, 64, 128),       # odd size, two channel blocks
     (1, 28, 28, 128, 96),     # K not a multiple of 64
@@ -76,7 +76,7 @@ def test_tf32_matches_fp32_path_closely(wg, oracle):
 
 
 def test_pruned_weights_and_block_skipping(wg, oracle):
-    """Unstructured mask (density 0.3, as in BASELINE config 3) and a block-structured mask whose
+    """Unstructured mask (density 0.3, the conv4_x benchmark shape) and a block-structured mask whose
     all-zero 64x32 blocks are skipped by the kernel: both must equal the dense arithmetic."""
     shape = (2, 14, 14, 256, 256)
     B, H, W, C, K = shape
