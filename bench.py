@@ -228,7 +228,7 @@ def run_resnet(args, rank, world, local):
     total = args.batch if args.batch > 0 else 256
     lo, hi = wg2x2.shard.shard_range(total, world, rank)
     n = hi - lo
-    model = ResNet18Var(stage5_pool=not args.stage5_at_14, math=args.math).to(dev).eval()
+    model = ResNet18Var(stage5_pool=not args.stage5_at_14, math=args.math, layout=args.net_layout).to(dev).eval()
     gen = torch.Generator().manual_seed(100 + rank)
     imgs_h = torch.randn((n, 3, 224, 224), generator=gen).pin_memory()
     imgs = [imgs_h.to(dev) + 0.0 * i for i in range(2)]
@@ -309,7 +309,7 @@ def run_resnet(args, rank, world, local):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
             "config": {"workload": "cfg4", "total_batch": total, "per_gpu_batch": n, "image": 224,
-                       "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": "NCHW",
+                       "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": args.net_layout,
                        "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; stem, pools, 1x1 shortcuts, BN, FC on stock torch",
                        "l2": "two rotating image batches; activations of a step exceed L2 many times over",
                        "launch": "eager" if graphs is None else "one CUDA graph per input buffer"},
@@ -336,6 +336,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
     ap.add_argument("--e2e-chunks", type=int, default=2, help="chunks of the host-buffer pipeline")
     ap.add_argument("--fused", action="store_true", help="time the one-kernel layer (X -> Y, V never stored) instead of the two kernels")
+    ap.add_argument("--net-layout", default="NHWC", choices=["NHWC", "NCHW"], help="cfg4: physical layout of the activations")
     ap.add_argument("--no-graph", action="store_true", help="cfg4: launch the network eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

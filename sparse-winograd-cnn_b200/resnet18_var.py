@@ -22,13 +22,11 @@ DENSITY = (0.6, 0.4, 0.3, 0.2)                               # Winograd-domain w
 
 
 def _same_pool(x):
-    """MaxPooling(3, stride=2, padding='SAME') of TensorFlow: for even sizes the one pad row/column goes
-    at the bottom/right."""
+    """MaxPooling(3, stride=2, padding='SAME') of TensorFlow without a padded copy.  For an even size TF pads one
+    row/column at the bottom/right only (windows 2i..2i+2, the last one clipped): that is ceil_mode with no
+    padding.  For an odd size it pads one on each side: padding=1."""
     H, W = x.shape[2], x.shape[3]
-    ph = max((-(-H // 2) - 1) * 2 + 3 - H, 0)
-    pw = max((-(-W // 2) - 1) * 2 + 3 - W, 0)
-    x = F.pad(x, (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2), value=float("-inf"))
-    return F.max_pool2d(x, 3, 2)
+    return F.max_pool2d(x, 3, 2, padding=(H % 2, W % 2), ceil_mode=True)
 
 
 class _BN(torch.nn.Module):
@@ -61,21 +59,35 @@ class _WinogradLayer(torch.nn.Module):
             self._prepared = wg2x2.prepare_weights(self.W)
         return self._prepared
 
-    def forward(self, x, math="tf32"):
-        B, C, H, W = x.shape
-        v = wg2x2.imtrans_fwd(x.contiguous(), relu=True, layout="NCHW")
-        if math == "tf32":
-            return wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout="NCHW")
-        return wg2x2.conv_fwd(v, self.W, H, W, layout="NCHW", math="fp32")
+    @staticmethod
+    def _to_kernel(x, layout):
+        """(B,C,H,W)-shaped activation -> the contiguous tensor the kernels take: itself for NCHW, the (B,H,W,C)
+        view of a channels-last tensor for NHWC (no copy when x already is channels-last)."""
+        return x.contiguous() if layout == "NCHW" else x.permute(0, 2, 3, 1).contiguous()
 
-    def forward_fused(self, x, bn_in, bn_out=None, residual=None):
+    @staticmethod
+    def _from_kernel(y, layout):
+        return y if layout == "NCHW" else y.permute(0, 3, 1, 2)     # channels-last view of the (B,H,W,K) result
+
+    def forward(self, x, math="tf32", layout="NCHW"):
+        B, C, H, W = x.shape
+        v = wg2x2.imtrans_fwd(self._to_kernel(x, layout), relu=True, layout=layout)
+        if math == "tf32":
+            y = wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout=layout)
+        else:
+            y = wg2x2.conv_fwd(v, self.W, H, W, layout=layout, math="fp32")
+        return self._from_kernel(y, layout)
+
+    def forward_fused(self, x, bn_in, bn_out=None, residual=None, layout="NCHW"):
         """BatchNorm -> transform + ReLU -> product [-> BatchNorm + shortcut add] in two kernels: bn_in folds
         into the transform's load, bn_out and the residual into the product's epilogue (tensor-core path)."""
         B, C, H, W = x.shape
-        v = wg2x2.imtrans_fwd(x.contiguous(), relu=True, layout="NCHW", in_scale=bn_in.scale, in_shift=bn_in.shift)
-        return wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout="NCHW",
-                                       out_scale=None if bn_out is None else bn_out.scale,
-                                       out_shift=None if bn_out is None else bn_out.shift, residual=residual)
+        v = wg2x2.imtrans_fwd(self._to_kernel(x, layout), relu=True, layout=layout, in_scale=bn_in.scale, in_shift=bn_in.shift)
+        y = wg2x2.conv_fwd_prepared(v, self.prepared(), self.cout, H, W, layout=layout,
+                                    out_scale=None if bn_out is None else bn_out.scale,
+                                    out_shift=None if bn_out is None else bn_out.shift,
+                                    residual=None if residual is None else self._to_kernel(residual, layout))
+        return self._from_kernel(y, layout)
 
     def forward_reference(self, x):
         """The same layer from the transform matrices with float64 einsums (for tests)."""
@@ -92,10 +104,13 @@ class _WinogradLayer(torch.nn.Module):
 
 
 class ResNet18Var(torch.nn.Module):
-    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32", fused=True):
+    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32", fused=True, layout="NHWC"):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
         self.math = math
+        # physical layout of the activations: "NHWC" keeps them channels-last (the reference's layout, and the one
+        # both cuDNN's and this library's kernels like best), "NCHW" keeps torch's default
+        self.layout = layout
         self.fused = fused      # fold BatchNorms and shortcut additions into the Winograd kernels (tensor-core path)
         self.stage5_pool = stage5_pool
         self.stem = torch.nn.Parameter(torch.randn((64, 3, 7, 7), generator=gen) * (2.0 / (49 * 64)) ** 0.5, requires_grad=False)
@@ -117,9 +132,9 @@ class ResNet18Var(torch.nn.Module):
     def _block(self, blk, l, main, ref):
         """main + bn2c(conv(bn2b(conv(bn2a(l))))) with the Winograd layers as `ref` says."""
         if not ref and self.math == "tf32" and self.fused:
-            t = blk["w2a"].forward_fused(l, blk["bn2a"])
-            return blk["w2b"].forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main.contiguous())
-        conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math))
+            t = blk["w2a"].forward_fused(l, blk["bn2a"], layout=self.layout)
+            return blk["w2b"].forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main, layout=self.layout)
+        conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math, self.layout))
         t = conv(blk["w2a"], blk["bn2a"](l))
         t = conv(blk["w2b"], blk["bn2b"](t))
         return main + blk["bn2c"](t)
@@ -127,7 +142,12 @@ class ResNet18Var(torch.nn.Module):
     def forward(self, image, reference=False):
         """image: (B,3,H,W) float32, already normalised.  reference=True computes the Winograd layers with
         float64 einsums instead of this repository's kernels."""
-        l = F.conv2d(F.pad(image, (2, 3, 2, 3)), self.stem, stride=2)   # 7x7/2 with TensorFlow's SAME padding
+        x = F.pad(image, (2, 3, 2, 3))                                  # 7x7/2 with TensorFlow's SAME padding
+        stem = self.stem
+        if self.layout == "NHWC" and not reference:
+            x = x.contiguous(memory_format=torch.channels_last)
+            stem = stem.contiguous(memory_format=torch.channels_last)
+        l = F.conv2d(x, stem, stride=2)
         l = _same_pool(l)
         for s, (blk_a, blk_b) in enumerate(self.blocks):
             main = torch.relu(blk_a["pre"](l)) if s == 0 else torch.relu(l)

@@ -6,12 +6,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 @pytest.mark.parametrize("math,tol,fused", [("fp32", 2e-4, False), ("tf32", 2e-2, False), ("tf32", 2e-2, True)])
 @pytest.mark.parametrize("stage5_pool", [True, False])
-def test_forward_matches_einsum_graph(math, tol, fused, stage5_pool):
+def test_forward_matches_einsum_graph(math, tol, fused, stage5_pool, layout):
     from resnet18_var import ResNet18Var
     torch.manual_seed(0)
-    model = ResNet18Var(stage5_pool=stage5_pool, seed=3, math=math, fused=fused).cuda().eval()
+    model = ResNet18Var(stage5_pool=stage5_pool, seed=3, math=math, fused=fused, layout=layout).cuda().eval()
     x = torch.randn((2, 3, 96, 96), device="cuda")       # 24x24 at stage 2 ... 3x3 (odd) at stage 5
     with torch.no_grad():
         got = model(x)
@@ -44,3 +45,15 @@ def test_load_weights_and_masks_by_reference_names():
     x = torch.randn((1, 3, 64, 64), device="cuda")
     with torch.no_grad():
         assert torch.isfinite(model(x)).all()
+
+
+def test_same_pool_matches_tensorflow_padding():
+    """3x3/2 SAME max-pool: explicit -inf padding as TensorFlow places it vs the copy-free form used by the model."""
+    import torch.nn.functional as F
+    from resnet18_var import _same_pool
+    for H, W in [(112, 112), (7, 7), (14, 9), (5, 8)]:
+        x = torch.randn(2, 3, H, W)
+        ph = max((-(-H // 2) - 1) * 2 + 3 - H, 0)
+        pw = max((-(-W // 2) - 1) * 2 + 3 - W, 0)
+        ref = F.max_pool2d(F.pad(x, (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2), value=float("-inf")), 3, 2)
+        assert torch.equal(_same_pool(x), ref)
