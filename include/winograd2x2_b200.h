@@ -171,9 +171,10 @@ size_t wg2x2_layer_fwd_workspace_bytes(int B, int H, int W, int C, int K, int ma
 /*
  * Whole layer forward with prepared weights (tensor-core path), the call pair of
  * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119 in its fastest form for the shape:
- *  - one kernel (wg2x2_layer_fwd_fused) where that is supported (NCHW, W % 4 == 0, C % 16 == 0) and either
- *    C <= 64 or no V_scratch was given: transform and ReLU happen on the SM, the transformed input is never
- *    written to memory;
+ *  - one kernel (wg2x2_layer_fwd_fused) where that is supported (NCHW, W % 4 == 0, C % 16 == 0, X and Y
+ *    16-byte aligned) and either it is the faster one (K <= 128, or K <= 256 with C <= 64) or no V_scratch
+ *    was given: both transforms and the ReLU happen on the SM, neither the transformed input nor the
+ *    products are written to memory;
  *  - otherwise the two kernels with V_scratch (16*B*nH*nW*C floats) in between; WG2X2_ERR_WORKSPACE if NULL.
  * out_scale/out_shift/residual as in wg2x2_conv_fwd_prepared_fused (each may be NULL).
  */

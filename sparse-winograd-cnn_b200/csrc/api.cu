@@ -213,9 +213,12 @@ int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, flo
     if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
     if (!layout_ok(layout)) return WG2X2_ERR_BAD_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    // The one-kernel path wins where the product is cheap next to the V round trip (few channels); with more
-    // channels its on-SM transform, bound by instruction issue, is slower than the two HBM-bound kernels.
-    if (fused_fwd_supported(B, H, W, C, K, layout) && (C <= 64 || !V_scratch))
+    // The one-kernel path redoes the input transform for every block of 64 output channels, so it wins while
+    // there are few of them (measured: K <= 128, or K <= 256 with C <= 64); beyond that the two-kernel path,
+    // whose wide GEMM shares one transformed input among 256 output channels, is faster.
+    const bool fused_pays = K <= 128 || (K <= 256 && C <= 64);
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15u) == 0;   // TMA both ways
+    if (fused_fwd_supported(B, H, W, C, K, layout) && aligned16 && (fused_pays || !V_scratch))
         return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, out_scale, out_shift, residual, st);
     if (!V_scratch) return WG2X2_ERR_WORKSPACE;
     const int nH = (H + 1) / 2, nW = (W + 1) / 2;

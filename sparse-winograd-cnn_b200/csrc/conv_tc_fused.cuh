@@ -1,40 +1,63 @@
-// Fused Winograd-ReLU layer forward, X -> Y in one kernel (NCHW in and out): the transformed input V never
-// goes to memory.  Included by conv_tc.cu.
+// Fused Winograd-ReLU layer forward, X -> Y in one kernel (NCHW in and out): neither the transformed input V
+// nor the 16 Winograd-domain products ever exist outside the SM.  Included by conv_tc.cu.
 //
-// Same row walk as conv_fwd_tc_kernel (four 128x64 accumulators per Winograd row, double-buffered in TMEM,
-// A^T m A in the epilogue), but the A operand of every MMA is produced on the SM:
-//   * the X producer (warp 0) brings, by TMA, the input rows one Winograd row of a block of tiles needs, for
-//     16 channels at a time, into one of three shared-memory buffers; out-of-image rows and columns arrive as
-//     zeros, which is the layer's padding;
-//   * sixteen transform warps (one thread = one tile x 4 channels) read their 2 x 4 pixels per channel from
-//     that buffer, form the four values of Winograd row i of B^T d B, apply the ReLU, round to TF32 and write
-//     them into the four [128 x 16] A tiles of the stage ring in the 64-byte-swizzled K-major layout UMMA
-//     reads (the transform is bound by instruction issue, hence the many warps);
-//   * the W producer (warp 2) brings the matching [64 x 16] weight tiles by TMA;
-//   * the MMA issuer (warp 1) and the eight epilogue warps work as in the unfused kernel.
-// A unit is NB images x TH tile rows x TW tile columns (at most 128 tiles, one TMEM lane each) x 64 output
-// channels.  Each input row is fetched once per Winograd row that uses it (from L2 after the first time);
-// HBM sees X once and Y once.
+// Both transforms ride on the tensor core's operands:
+//   * input side: the A operand of every MMA (row i, column j of B^T d B for 128 tiles x 16 channels, after
+//     the ReLU) is computed by the transform warps and written with tcgen05.st into tensor memory
+//     (lane = tile, column = channel); tcgen05.mma reads it from there;
+//   * output side: y[a][e] = sum_ij At[a][i] At[e][j] (V_ij . W_ij) is linear in the products and the
+//     coefficients are 0 / +1 / -1, so position (i, j) is accumulated straight into the (up to four) output
+//     accumulators (a, e) it contributes to, with the instruction descriptor's negate bit for the minus
+//     signs.  That costs 36 instead of 16 MMAs per 8 channels (the tensor core has the room) and leaves four
+//     128x64 accumulators per unit instead of sixteen products: the epilogue only copies.
+// One step = one Winograd row i of one block of tiles for 16 input channels:
+//   * the X producer (warp 0) brings, by TMA, the input rows that step needs into a ring of shared-memory
+//     buffers: rows d1,d2 of every tile for i = 1, 2 (a dense box), rows d0,d2 (i = 0) or d1,d3 (i = 3) through
+//     a tensor map that walks the image with a row stride of 2, so only the rows that are used travel;
+//     out-of-image rows and columns arrive as zeros, which is the layer's padding;
+//   * two teams of eight transform warps take alternate steps (while one team waits for loads or for the
+//     tensor core, the other issues); a thread owns one tile x 8 channels;
+//   * the W producer (warp 2) streams the step's four [64 x 16] weight tiles (B operands) into the same ring
+//     slot the A group belongs to;
+//   * two MMA issuers (warps 1 and 3), one per output column e: a single issuing thread gets too few issue
+//     slots next to the transform warps to keep the tensor core fed, and each accumulator has one owner.
+//     (Roles must not share a warp: a lane that waits on an mbarrier stalls the other lanes of its warp too.)
+//   * the eight epilogue warps read output row a = 0 as soon as Winograd row 2 is done (row 3 does not touch
+//     it) and row a = 1 after row 3, stage 16 channels at a time in shared memory and hand the box to a TMA
+//     store (row stride 2 in Y), which also clips odd sizes and partial blocks.
+// Tensor memory: columns 0..255 = the accumulators (a, e) at (2a + e) * 64, 256..511 = a ring of four A
+// groups (4 tiles x 16 columns each).  A unit is NB images x TH tile rows x TW tile columns (at most 128
+// tiles, one TMEM lane each) x 64 output channels.  Each input row is fetched once per Winograd row that uses
+// it (from L2 after the first time); HBM sees X once and Y once.
 #pragma once
 
-constexpr int kFuStages = 8;                       // two groups of four (one per Winograd column j)
-constexpr int kFuABytes = 128 * 64;                // [128 tiles][16 channels] fp32
-constexpr int kFuBBytes = 64 * 64;                 // [64 out-channels][16 channels]
-constexpr int kFuStageBytes = kFuABytes + kFuBBytes;
+constexpr int kFuAGroups = 4;                      // ring of A groups in tensor memory; a group = four [128 x 16] tiles
+constexpr int kFuACol0 = 4 * kBlockN;              // first tensor-memory column of the A ring
+constexpr int kFuWStages = kFuAGroups;            // a W stage travels with its A group: one "slot" of the ring
+constexpr int kFuWBytes = 4 * 64 * 64;             // four (one per j) [64 out-channels][16 channels] tiles
 constexpr int kFuXbufs = 3;
-constexpr int kFuXbufBytes = 40960;
-constexpr int kFuXfWarps = 16;                     // transform warps: one thread = one tile x 4 channels of a group
-constexpr int kFuThreads = 128 + 256 + 32 * kFuXfWarps;   // control WG, 2 epilogue WGs, 4 transform WGs
-constexpr int kFuSmemBytes = kFuStages * kFuStageBytes + kFuXbufs * kFuXbufBytes + kCtrlBytes + 1024;
+constexpr int kFuXbufBytes = 32768;
+constexpr int kFuTeamWarps = 8;                    // transform warps per team: one thread = one tile x 8 channels
+constexpr int kFuThreads = 256 + 256 + 2 * 32 * kFuTeamWarps;   // 2 control WGs, 2 epilogue WGs, 2 transform teams (2 WGs each)
+constexpr int kFuYStageBytes = kFuXbufBytes;      // per epilogue warpgroup: two [NB][16 channels][TH rows][2*TW pixels] boxes of Y
+constexpr int kFuSmemBytes = kFuWStages * kFuWBytes + kFuXbufs * kFuXbufBytes + 2 * kFuYStageBytes + kCtrlBytes + 1024;
+static_assert(kFuACol0 + kFuAGroups * 64 <= (int)kTmemCols, "tensor memory columns");
+static_assert(kFuSmemBytes <= 232448, "shared memory per CTA");
+// Register hand-over (setmaxnreg): the kernel starts with 64 registers per thread; the increase of the transform
+// warps can only be served from what the other warps of the same CTA have given back, and it blocks (for
+// ever) if that is not enough, so the three shares must fit into the launch allocation.
+constexpr int kFuRegsLaunch = 64, kFuRegsCtrl = 24, kFuRegsXf = 80, kFuRegsEpi = 64;
+static_assert(256 * kFuRegsCtrl + 256 * kFuRegsEpi + 2 * 32 * kFuTeamWarps * kFuRegsXf <= kFuRegsLaunch * kFuThreads,
+              "setmaxnreg shares exceed the registers the CTA was launched with");
 
 struct FuParams {
     float *Y;
     const float *out_scale, *out_shift, *residual;
     int B, H, W, C, K, nH, nW, outH, outW;
-    int TH, TW, NB, BH, BW;          // block of tiles and the input box that feeds one Winograd row of it
+    int TH, TW, NB, BW, BWY;         // block of tiles; BW = width of the input box, BWY = of the output box
     int nRB, nSeg, nGroups, nKB, nC16;
     int units, relu;
-    uint32_t xbytes;
+    uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows) and of the row-stride-2 (TH+1 rows) box
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
@@ -42,6 +65,29 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// Bounded wait for roles that can afford a late wake-up: sleeps between polls, so that the waiting warp leaves
+// the issue slots of its scheduler to the warps that have work.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where, unsigned ns)
+{
+    for (long long it = 0; it < kSpinLimit / 8; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(ns);
+        if ((it & 255) == 255 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    g_tc_status[1] = where;
+    g_tc_status[0] = 1;
+    return false;
+}
+
+// shared memory -> global, clipped to the tensor; completion is tracked by the thread's bulk async-groups
+__device__ __forceinline__ void tma_store_4d(uint32_t src, const CUtensorMap *map, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%1, {%2, %3, %4, %5}], [%0];"
+        ::"r"(src), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // K-major operand with rows of 64 bytes, 64-byte swizzle: 8-row groups 512 B apart
@@ -56,34 +102,79 @@ __device__ __forceinline__ uint64_t make_desc_k_sw64(uint32_t smem_addr)
     return d;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem], M=128, N=kBlockN, K=8 (tf32): A is 128 lanes x 8 columns of tensor memory
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The two K=8 MMAs of one [128 x 16] A tile: columns a_tmem.. and a_tmem+8.., B descriptors 32 bytes apart.
+// The first accumulates only if `accumulate`, the second always.
+__device__ __forceinline__ void umma_tf32_ts_x2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 b0, b1;\n\t.reg .b32 a1, l1;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.eq.b32 q, %4, %4;\n\t"
+        "mov.b64 b0, {%2, %3};\n\t"
+        "add.u32 l1, %2, 2;\n\t"
+        "mov.b64 b1, {l1, %3};\n\t"
+        "add.u32 a1, %1, 8;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], b0, %4, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [a1], b1, %4, q;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 4 registers per thread -> this warp's 32 lanes x 4 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const float *r)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
+                 ::"r"(taddr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3]))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 template <bool EXTRAS>
 __global__ void __launch_bounds__(kFuThreads, 1)
-layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const FuParams prm)
+layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
+                       const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapY, const FuParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen_base = smem_raw + (base - raw);
-    const uint32_t xbase = base + kFuStages * kFuStageBytes;
-    const float *xgen = reinterpret_cast<const float *>(gen_base + kFuStages * kFuStageBytes);
-    const uint32_t bars = xbase + kFuXbufs * kFuXbufBytes;
-    uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kFuStages * kFuStageBytes + kFuXbufs * kFuXbufBytes);
-    // barriers: full[8], empty[8], acc_full[2], acc_empty[2], xfull[3], xempty[3]
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (kFuStages + s); };
-    auto accf_bar = [&](int b) { return bars + 8u * (2 * kFuStages + b); };
-    auto acce_bar = [&](int b) { return bars + 8u * (2 * kFuStages + 2 + b); };
-    auto xfull_bar = [&](int b) { return bars + 8u * (2 * kFuStages + 4 + b); };
-    auto xempty_bar = [&](int b) { return bars + 8u * (2 * kFuStages + 4 + kFuXbufs + b); };
-    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + 2 * kFuStages + 4 + 2 * kFuXbufs);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kFuStages + 5 + 2 * kFuXbufs);
+    constexpr int kWOff = 0;
+    constexpr int kXOff = kWOff + kFuWStages * kFuWBytes;
+    constexpr int kYOff = kXOff + kFuXbufs * kFuXbufBytes;
+    constexpr int kBarOff = kYOff + 2 * kFuYStageBytes;
+    const uint32_t wbase = base + kWOff, xbase = base + kXOff, bars = base + kBarOff;
+    const float *xgen = reinterpret_cast<const float *>(gen_base + kXOff);
+    uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
+    // barriers: full[G] (A group written by a team + its W tiles landed), free[G] (the four issuers' MMAs on the
+    // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[XB], xempty[XB], ywritten[2], yfree[2]
+    constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
+                  kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXbufs, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
+    static_assert((kB8 + 2) * 8 <= kCtrlBytes, "control block");
+    auto full_bar = [&](int g) { return bars + 8u * (kB0 + g); };
+    auto free_bar = [&](int g) { return bars + 8u * (kB1 + g); };
+    auto accf_bar = [&](int b) { return bars + 8u * (kB4 + b); };
+    auto acce_bar = [&](int b) { return bars + 8u * (kB5 + b); };
+    auto xfull_bar = [&](int b) { return bars + 8u * (kB6 + b); };
+    auto xempty_bar = [&](int b) { return bars + 8u * (kB7 + b); };
+    auto ywritten_bar = [&](int h) { return bars + 8u * (kB7b + h); };
+    auto yfree_bar = [&](int h) { return bars + 8u * (kB7b + 2 + h); };
+    volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + kB8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + kB8 + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kFuStages; ++s) { mbar_init(full_bar(s), 1 + kFuXfWarps); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
-        for (int b = 0; b < kFuXbufs; ++b) { mbar_init(xfull_bar(b), 1); mbar_init(xempty_bar(b), kFuXfWarps); }
+        for (int g = 0; g < kFuAGroups; ++g) { mbar_init(full_bar(g), kFuTeamWarps + 1); mbar_init(free_bar(g), 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 2); mbar_init(acce_bar(b), kEpiWarps); }
+        for (int b = 0; b < kFuXbufs; ++b) { mbar_init(xfull_bar(b), 1); mbar_init(xempty_bar(b), kFuTeamWarps); }
+        for (int h = 0; h < 2; ++h) { mbar_init(ywritten_bar(h), 4); mbar_init(yfree_bar(h), 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -104,10 +195,58 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_co
         g = u / prm.nRB;
     };
 
-    // registers: 896 threads x 72 at launch; control warps keep 24, transform warps 40, epilogue warps take 160
-    if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
-        if (warp == 0 && lane == 0) {
+    // registers: 1024 threads x 64 at launch; control warps keep 24, epilogue warps stay at 64, transform warps take 80
+    if (warp < 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFuRegsCtrl));
+        if (warp < 4 && lane == 0) {
+            // ------------------------------ MMA issuers -----------------------------------
+            // Issuer (a, e) = warp (2a + e) owns that accumulator: position (i, j) goes into it with the sign
+            // At[a][i] * At[e][j]; At = [[1,1,1,0],[0,1,-1,-1]], so column e takes j = e..e+2 and row a takes
+            // i = a..a+2.  On the one row it has nothing to add the issuer still follows the ring (wait, commit).
+            constexpr uint32_t idesc_pos = make_idesc_tf32(kBlockM, kBlockN);
+            constexpr uint32_t idesc_neg = idesc_pos | (1u << 14);            // negate B
+            const int a = warp >> 1, e = warp & 1;
+            const uint32_t d_tmem = tmem_base + (uint32_t)(warp * kBlockN);
+            const uint32_t a_tmem0 = tmem_base + (uint32_t)(kFuACol0 + e * 16);
+            const uint64_t bdesc0 = make_desc_k_sw64(wbase + e * (kFuWBytes / 4));
+            const uint32_t b_hi = (uint32_t)(bdesc0 >> 32), b_lo0 = (uint32_t)bdesc0;
+            const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int total = my_units * 4 * nC16;
+            int g = 0; uint32_t gph = 0;
+            int i = 0, cc = 0;
+            uint32_t units_done = 0;
+            int trm = 0; (void)trm;
+            // the slot's barrier is probed one step ahead, so that the probe's latency hides behind the MMAs
+            bool ready = total > 0 && mbar_try_wait(full_bar(0), 0);
+            for (int n = 0; n < total; ++n) {
+                if (warp == 0) TC_TRACE(1024 + 5 * trm);
+                if (!ready && !mbar_wait(full_bar(g), gph, abort_flag, 0x300u | g)) break;
+                if (warp == 0) TC_TRACE(1024 + 5 * trm + 1);
+                // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
+                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x200u | warp)) break;
+                if (warp == 0) TC_TRACE(1024 + 5 * trm + 2);
+                tc_fence_after();
+                int g2 = g + 1; uint32_t gph2 = gph;
+                if (g2 == kFuAGroups) { g2 = 0; gph2 ^= 1u; }
+                ready = (n + 1 < total) && mbar_try_wait(full_bar(g2), gph2);
+                if (i >= a && i <= a + 2) {
+                    const bool neg_a = (a == 1 && i >= 2);
+                    const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * 64), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
+#pragma unroll
+                    for (int jj = 0; jj < 3; ++jj) {
+                        const bool neg_e = (e == 1 && jj >= 1);                      // At[1][j] = -1 for j = 2, 3
+                        umma_tf32_ts_x2(d_tmem, a_tmem + (uint32_t)(jj * 16), b_lo + (uint32_t)(jj * (kFuWBytes / 4 >> 4)), b_hi,
+                                        (neg_a != neg_e) ? idesc_neg : idesc_pos, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
+                    }
+                }
+                if (warp == 0) TC_TRACE(1024 + 5 * trm + 3);
+                umma_commit(free_bar(g));
+                if (cc == nC16 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
+                if (warp == 0) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
+                g = g2; gph = gph2;
+                if (++cc == nC16) { cc = 0; if (++i == 4) { i = 0; ++units_done; } }
+            }
+        } else if (warp == 4 && lane == 0) {
             // ------------------------------ X producer -----------------------------------
             int xb = 0; uint32_t xph = 0;
             bool ok = true;
@@ -117,19 +256,22 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_co
                 decode(u, g, rb, seg, kb);
                 const int x0 = 2 * seg * prm.TW - 4, th0 = rb * prm.TH, b0 = g * prm.NB;
                 for (int i = 0; i < 4 && ok; ++i) {
+                    const bool strided = (i == 0 || i == 3);
                     const int h_lo = 2 * th0 - (i == 0 ? 1 : 0);
+                    const CUtensorMap *map = strided ? &mapX2 : &mapX1;
+                    const uint32_t bytes = strided ? prm.xbytes2 : prm.xbytes1;
                     for (int cc = 0; cc < nC16; ++cc) {
-                        if (!mbar_wait(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb)) { ok = false; break; }
+                        if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100)) { ok = false; break; }
                         TC_TRACE(trx); ++trx;
-                        mbar_expect_tx(xfull_bar(xb), prm.xbytes);
-                        tma_load_4d(xbase + xb * kFuXbufBytes, &mapX, xfull_bar(xb), x0, h_lo, cc * 16, b0);
+                        mbar_expect_tx(xfull_bar(xb), bytes);
+                        tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xb), x0, h_lo, cc * 16, b0);
                         if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
                     }
                 }
             }
             if (!ok)
                 for (int it = 0; it < 1000; ++it) __nanosleep(1000);
-        } else if (warp == 2 && lane == 0) {
+        } else if (warp == 6 && lane == 0) {
             // ------------------------------ W producer -----------------------------------
             int s = 0; uint32_t ph = 0;
             bool ok = true;
@@ -137,212 +279,182 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_co
                 int g, rb, seg, kb;
                 decode(u, g, rb, seg, kb);
                 for (int i = 0; i < 4 && ok; ++i)
-                    for (int cc = 0; cc < nC16 && ok; ++cc)
-                        for (int j = 0; j < 4; ++j) {
-                            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0xA00u | s)) { ok = false; break; }
-                            mbar_expect_tx(full_bar(s), kFuBBytes);
-                            tma_load_3d(base + s * kFuStageBytes + kFuABytes, &mapW, full_bar(s), cc * 16, kb * kBlockN, 4 * i + j);
-                            if (++s == kFuStages) { s = 0; ph ^= 1u; }
-                        }
+                    for (int cc = 0; cc < nC16; ++cc) {
+                        if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100)) { ok = false; break; }
+                        mbar_expect_tx(full_bar(s), kFuWBytes);
+                        tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), cc * 16, kb * kBlockN, 4 * i);
+                        if (++s == kFuWStages) { s = 0; ph ^= 1u; }
+                    }
             }
             if (!ok)
                 for (int it = 0; it < 1000; ++it) __nanosleep(1000);
-        } else if (warp == 1 && lane == 0) {
-            // ------------------------------ MMA issuer -----------------------------------
-            constexpr uint32_t idesc = make_idesc_tf32(kBlockM, kBlockN);
-            int s = 0; uint32_t ph = 0;
-            uint32_t acc_use[2] = {0, 0};
-            bool ok = true;
-            for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
-                for (int i = 0; i < 4 && ok; ++i) {
-                    const int buf = i & 1;
-                    if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf)) { ok = false; break; }
-                    acc_use[buf]++;
-                    tc_fence_after();
-                    for (int cc = 0; cc < nC16 && ok; ++cc)
-                        for (int j = 0; j < 4; ++j) {
-                            if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s)) { ok = false; break; }
-                            tc_fence_after();
-                            const uint32_t a_addr = base + s * kFuStageBytes;
-                            const uint64_t adesc = make_desc_k_sw64(a_addr);
-                            const uint64_t bdesc = make_desc_k_sw64(a_addr + kFuABytes);
-                            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 4 * kBlockN + j * kBlockN);
-#pragma unroll
-                            for (int kk = 0; kk < 2; ++kk)
-                                umma_tf32(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (cc > 0 || kk > 0) ? 1u : 0u);
-                            umma_commit(empty_bar(s));
-                            if (++s == kFuStages) { s = 0; ph ^= 1u; }
-                        }
-                    if (ok) umma_commit(accf_bar(buf));
-                }
-            }
         }
-    } else if (warp >= 12) {
-        // ------------------------------ transform warps ----------------------------------
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-        const int l = ((warp - 12) & 3) * 32 + lane;           // tile = TMEM lane = A-tile row
-        const int c4 = (warp - 12) >> 2;                       // which 4 of the group's 16 channels
+    } else if (warp >= 16) {
+        // ------------------------------ transform teams ----------------------------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kFuRegsXf));
+        const int team = (warp - 16) / kFuTeamWarps;
+        const int tw8 = (warp - 16) % kFuTeamWarps;
+        const int l = (tw8 & 3) * 32 + lane;                   // tile = TMEM lane = A-tile row
+        const int hq = tw8 >> 2;                               // which 8 of the step's 16 channels
         const int per_img = prm.TH * prm.TW;
         const bool live = l < prm.NB * per_img;
         const int le = live ? l : 0;                            // dead lanes (block smaller than 128 tiles) shadow tile 0:
         const int bi = le / per_img, rem = le - bi * per_img;   // their A rows feed TMEM lanes nobody reads
         const int thl = rem / prm.TW, twl = rem - thl * prm.TW;
-        const bool edge_l = (lane == 0) || (twl == 0) || !live;
-        const bool edge_r = (lane == 31) || (twl == prm.TW - 1) || !live;
-        const int BH = prm.BH, BW = prm.BW;
-        const uint32_t swz = (uint32_t)((l >> 1) & 3);
-        int xb = 0; uint32_t xph = 0;
-        int s = 0; uint32_t ph = 0;
+        const int BW = prm.BW;
+        const float lo = prm.relu ? 0.f : -__int_as_float(0x7f800000);
+        const int spu = 4 * nC16;                               // steps per unit
+        const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int total = my_units * spu;
+        // step n uses X buffer n % kFuXbufs and A group n % kFuAGroups; this team takes n = team, team + 2, ...
+        int xb = team % kFuXbufs, g = team % kFuAGroups, r = team;
+        uint32_t xph = 0, gph = 0;
         bool ok = true;
         int trt = 0; (void)trt;
-        for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
-            for (int i = 0; i < 4 && ok; ++i) {
-                const int rowA = 2 * thl, rowB = 2 * thl + ((i == 0 || i == 3) ? 2 : 1);
-                for (int cc = 0; cc < nC16; ++cc) {
-                    if (warp == 12 && lane == 0) TC_TRACE(512 + 4 * trt);
-                    if (!mbar_wait(xfull_bar(xb), xph, abort_flag, 0xB00u | xb)) { ok = false; break; }
-                    if (warp == 12 && lane == 0) TC_TRACE(512 + 4 * trt + 1);
+        for (int n = team; n < total; n += 2) {
+            const int i = r / nC16;
+            const bool strided = (i == 0 || i == 3);
+            const int rows = strided ? prm.TH + 1 : 2 * prm.TH;
+            const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
+            const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
+            const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
+            if (!mbar_wait(xfull_bar(xb), xph, abort_flag, 0xB00u | xb)) { ok = false; break; }
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
+            if (!mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
+            const int chs = rows * BW;
+            const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
+            tc_fence_after();
+            const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * 64);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (ok && !mbar_wait(empty_bar(s + j), ph ^ 1u, abort_flag, 0xC00u | (s + j))) ok = false;
-                    if (!ok) break;
-                    if (warp == 12 && lane == 0) TC_TRACE(512 + 4 * trt + 2);
-                    const float *xb_ptr = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * BH) * BW + 2 * twl + 3;
-                    uint8_t *a_tiles = gen_base + s * kFuStageBytes + l * 64;
-                    {
-                        float o[4][4];   // [j][channel within the quad]
+            for (int q = 0; q < 2; ++q) {
+                const int c4 = 2 * hq + q;
+                float o[4][4];   // [j][channel within the quad]
 #pragma unroll
-                        for (int cq = 0; cq < 4; ++cq) {
-                            // each lane reads the two pixels its tile owns as one 8-byte load per row and takes the
-                            // two halo pixels from its neighbours' registers; only lanes at the edge of a tile row
-                            // (or of the warp) read them from shared memory
-                            const float *pa = xb_ptr + ((c4 * 4 + cq) * BH + rowA) * BW;
-                            const float *pb = xb_ptr + ((c4 * 4 + cq) * BH + rowB) * BW;
-                            const float2 am = *reinterpret_cast<const float2 *>(pa + 1);
-                            const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
-                            float a0 = __shfl_up_sync(0xffffffffu, am.y, 1), a3 = __shfl_down_sync(0xffffffffu, am.x, 1);
-                            float b0 = __shfl_up_sync(0xffffffffu, bm.y, 1), b3 = __shfl_down_sync(0xffffffffu, bm.x, 1);
-                            if (edge_l) { a0 = pa[0]; b0 = pb[0]; }
-                            if (edge_r) { a3 = pa[3]; b3 = pb[3]; }
-                            float r[4];
-                            if (i == 1)      { r[0] = a0 + b0; r[1] = am.x + bm.x; r[2] = am.y + bm.y; r[3] = a3 + b3; }
-                            else if (i == 2) { r[0] = b0 - a0; r[1] = bm.x - am.x; r[2] = bm.y - am.y; r[3] = b3 - a3; }
-                            else             { r[0] = a0 - b0; r[1] = am.x - bm.x; r[2] = am.y - bm.y; r[3] = a3 - b3; }
-                            float v0 = r[0] - r[2], v1 = r[1] + r[2], v2 = r[2] - r[1], v3 = r[1] - r[3];
-                            if (prm.relu) { v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f); v2 = fmaxf(v2, 0.f); v3 = fmaxf(v3, 0.f); }
-                            // stored as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
-                            o[0][cq] = v0; o[1][cq] = v1; o[2][cq] = v2; o[3][cq] = v3;
-                        }
-                        const uint32_t chunk = ((uint32_t)c4 ^ swz) << 4;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<float4 *>(a_tiles + j * kFuStageBytes + chunk) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
-                    }
-                    // make the generic-proxy writes visible to the tensor core's async proxy, then publish
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (warp == 12 && lane == 0) TC_TRACE(512 + 4 * trt + 3);
-                    ++trt;
-                    if (lane == 0) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) mbar_arrive(full_bar(s + j));
-                        mbar_arrive(xempty_bar(xb));
-                    }
-                    s += 4;
-                    if (s == kFuStages) { s = 0; ph ^= 1u; }
-                    if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
+                for (int cq = 0; cq < 4; ++cq) {
+                    // the tile's 4 pixels of rows a and b: the middle two as one 8-byte load, the outer two alone
+                    const float *pa = xq + (c4 * 4 + cq) * chs;
+                    const float *pb = pa + dab;
+                    const float2 am = *reinterpret_cast<const float2 *>(pa + 1);
+                    const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
+                    const float a0 = pa[0], a3 = pa[3], b0 = pb[0], b3 = pb[3];
+                    const float r0 = fmaf(sb, b0, a0), r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y), r3 = fmaf(sb, b3, a3);
+                    // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
+                    o[0][cq] = fmaxf(r0 - r2, lo);
+                    o[1][cq] = fmaxf(r1 + r2, lo);
+                    o[2][cq] = fmaxf(r2 - r1, lo);
+                    o[3][cq] = fmaxf(r1 - r3, lo);
                 }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 16 + c4 * 4), o[j]);
+                if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
             }
+            // the tensor-memory writes have to be complete before the MMA issuer is told
+            tmem_st_wait();
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 6);
+            tc_fence_before();
+            __syncwarp();
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 3);
+            ++trt;
+            if (lane == 0) {
+                mbar_arrive(full_bar(g));
+                mbar_arrive(xempty_bar(xb));
+            }
+            r += 2; if (r >= spu) r -= spu;
+            xb += 2; if (xb >= kFuXbufs) { xb -= kFuXbufs; xph ^= 1u; }
+            g += 2; if (g >= kFuAGroups) { g -= kFuAGroups; gph ^= 1u; }
         }
+        (void)ok;
     } else {
         // ------------------------------ epilogue ------------------------------------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
-        const int ew = warp - 4;
+        const int ew = warp - 8;                                 // (these warps keep the 64 registers of the launch)
         const int q = warp & 3;
-        const int half = ew >> 2;
+        const int half = ew >> 2;                                // which 32 of the 64 output channels
         const int l = q * 32 + lane;
         const int per_img = prm.TH * prm.TW;
-        const int bi = l / per_img, rem = l - bi * per_img;
+        const bool live = l < prm.NB * per_img;
+        const int le = live ? l : 0;
+        const int bi = le / per_img, rem = le - bi * per_img;
         const int thl = rem / prm.TW, twl = rem - thl * prm.TW;
-        uint32_t acc_use[2] = {0, 0};
+        const int BWY = prm.BWY, TH = prm.TH;
+        const int box_floats = prm.NB * 16 * TH * BWY;           // one staged box
+        float *stage0 = reinterpret_cast<float *>(gen_base + kYOff + half * kFuYStageBytes);
+        const int my_off = (bi * 16 * TH + thl) * BWY + 2 * twl; // this thread's tile in channel 0 of a box
+        const bool elected = ((ew & 3) == 0) && lane == 0;
+        uint32_t units_done = 0, st_use = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
             int g, rb, seg, kb;
             decode(u, g, rb, seg, kb);
-            float y[4][32];
-#pragma unroll
-            for (int o = 0; o < 4; ++o)
-#pragma unroll
-                for (int c = 0; c < 32; ++c) y[o][c] = 0.f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int buf = i & 1;
-                if (ok && !mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
-                acc_use[buf]++;
-                if (ok) {
-                    tc_fence_after();
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 4 * kBlockN + half * 32);
-#pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        float m[4][8];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) tmem_ld8(taddr + (uint32_t)(j * kBlockN + ch * 8), m[j]);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            float z0, z1;
-                            at_cols(m[0][c], m[1][c], m[2][c], m[3][c], z0, z1);
-                            if (i <= 2) { y[0][ch * 8 + c] += z0; y[1][ch * 8 + c] += z1; }
-                            if (i == 1) { y[2][ch * 8 + c] += z0; y[3][ch * 8 + c] += z1; }
-                            if (i >= 2) { y[2][ch * 8 + c] -= z0; y[3][ch * 8 + c] -= z1; }
-                        }
-                    }
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acce_bar(buf));
-                }
-            }
-            if (!ok) break;
-            const int b = g * prm.NB + bi, th = rb * prm.TH + thl, tw = seg * prm.TW + twl;
-            const bool tile_ok = (l < prm.NB * per_img) && b < prm.B && th < prm.nH && tw < prm.nW;
+            const int b = g * prm.NB + bi, th = rb * TH + thl, tw = seg * prm.TW + twl;
+            const bool tile_ok = live && b < prm.B && th < prm.nH && tw < prm.nW;
             const int kbase = kb * kBlockN + half * 32;
-            if (tile_ok) {
-                const bool pair = (prm.outW & 1) == 0;
-                const long long cstride = (long long)prm.outH * prm.outW;
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
-                    const int h = 2 * th + a;
-                    if (h >= prm.outH) continue;
-                    const long long o0 = (((long long)b * prm.K + kbase) * prm.outH + h) * prm.outW + 2 * tw;
+            for (int a = 0; a < 2; ++a) {
+                if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a);
+                if (!mbar_wait_sleepy(accf_bar(a), units_done & 1u, abort_flag, 0x400u | (ew << 4) | a, 400)) { ok = false; break; }
+                if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a + 1);
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 2 * kBlockN + half * 32);
 #pragma unroll
-                    for (int cg = 0; cg < 32; cg += 8) {
-                        float2 rs[8];
+                for (int rd = 0; rd < 2; ++rd) {
+                    float v0[16], v1[16];                         // pixels (a, 0) and (a, 1) of 16 channels
+                    tmem_ld8(taddr + (uint32_t)(rd * 16), v0);
+                    tmem_ld8(taddr + (uint32_t)(rd * 16 + 8), v0 + 8);
+                    tmem_ld8(taddr + (uint32_t)(kBlockN + rd * 16), v1);
+                    tmem_ld8(taddr + (uint32_t)(kBlockN + rd * 16 + 8), v1 + 8);
+                    tmem_ld_wait();
+                    if (rd == 1) {                                // output row a is in registers: hand its accumulators back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acce_bar(a));
+                    }
+                    // the store before last of this warpgroup has left its half of the staging area
+                    if (elected) {
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        mbar_arrive(yfree_bar(half));
+                    }
+                    if (!mbar_wait(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
+                    float *stage = stage0 + (st_use & 1u) * box_floats;
+                    if (live) {
+                        const int h = 2 * th + a;
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            rs[c] = make_float2(0.f, 0.f);
-                            if (EXTRAS && prm.residual && kbase + cg + c < prm.K) {
-                                const float *rp = prm.residual + o0 + (cg + c) * cstride;
-                                if (pair) rs[c] = __ldg(reinterpret_cast<const float2 *>(rp));
-                                else { rs[c].x = __ldg(rp); if (2 * tw + 1 < prm.outW) rs[c].y = __ldg(rp + 1); }
+                        for (int c = 0; c < 16; ++c) {
+                            const int k = kbase + rd * 16 + c;
+                            float y0 = v0[c], y1 = v1[c];
+                            if (EXTRAS && k < prm.K) {
+                                if (prm.out_scale) {
+                                    const float s1 = __ldg(prm.out_scale + k), b1 = __ldg(prm.out_shift + k);
+                                    y0 = fmaf(y0, s1, b1); y1 = fmaf(y1, s1, b1);
+                                }
+                                if (prm.residual && tile_ok && h < prm.outH) {
+                                    const float *rp = prm.residual + (((long long)b * prm.K + k) * prm.outH + h) * prm.outW + 2 * tw;
+                                    if ((prm.outW & 1) == 0) { const float2 r2 = __ldg(reinterpret_cast<const float2 *>(rp)); y0 += r2.x; y1 += r2.y; }
+                                    else { y0 += __ldg(rp); if (2 * tw + 1 < prm.outW) y1 += __ldg(rp + 1); }
+                                }
                             }
-                        }
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            if (kbase + cg + c >= prm.K) continue;
-                            float v0 = y[2 * a][cg + c], v1 = y[2 * a + 1][cg + c];
-                            if (EXTRAS && prm.out_scale) {
-                                const float s1 = __ldg(prm.out_scale + kbase + cg + c), b1 = __ldg(prm.out_shift + kbase + cg + c);
-                                v0 = fmaf(v0, s1, b1); v1 = fmaf(v1, s1, b1);
-                            }
-                            if (EXTRAS) { v0 += rs[c].x; v1 += rs[c].y; }
-                            float *dst = prm.Y + o0 + (cg + c) * cstride;
-                            if (pair) *reinterpret_cast<float2 *>(dst) = make_float2(v0, v1);
-                            else { dst[0] = v0; if (2 * tw + 1 < prm.outW) dst[1] = v1; }
+                            *reinterpret_cast<float2 *>(stage + my_off + c * TH * BWY) = make_float2(y0, y1);
                         }
                     }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(ywritten_bar(half));
+                    if (elected) {
+                        if (!mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew)) { ok = false; break; }
+                        if (kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
+                            tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                    ++st_use;
                 }
+                if (!ok) break;
             }
+            ++units_done;
         }
+        // the last boxes must have reached memory before the CTA ends
+        if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     tc_fence_before();
@@ -370,24 +482,29 @@ static bool fused_geometry(FuParams &p)
     p.TW = p.nW <= 32 ? p.nW : 32;
     p.nSeg = cdiv(p.nW, p.TW);
     p.BW = (2 * p.TW + 5 + 3) & ~3;
+    // the larger of the two boxes (2*TH rows x BW x 16 channels x NB images) has to fit an X buffer
+    auto box_bytes = [&](int th, int nb) { return (size_t)p.BW * 2 * th * 16 * 4 * nb; };
     int TH = kBlockM / p.TW;
     if (TH > p.nH) TH = p.nH;
-    while (TH > 1 && (size_t)p.BW * (2 * TH + 1) * 16 * 4 > (size_t)kFuXbufBytes) --TH;
-    if ((size_t)p.BW * (2 * TH + 1) * 16 * 4 > (size_t)kFuXbufBytes) return false;
+    while (TH > 1 && box_bytes(TH, 1) > (size_t)kFuXbufBytes) --TH;
+    if (box_bytes(TH, 1) > (size_t)kFuXbufBytes) return false;
+    p.nRB = cdiv(p.nH, TH);
+    TH = cdiv(p.nH, p.nRB);                  // same number of row blocks, evened out
     p.TH = TH;
-    p.BH = 2 * TH + 1;
     p.NB = 1;
     if (TH == p.nH) {
         int nb = kBlockM / (TH * p.TW);
-        while (nb > 1 && (size_t)p.BW * p.BH * 16 * 4 * nb > (size_t)kFuXbufBytes) --nb;
+        while (nb > 1 && box_bytes(TH, nb) > (size_t)kFuXbufBytes) --nb;
         if (nb > p.B) nb = p.B;
         p.NB = nb < 1 ? 1 : nb;
     }
-    p.nRB = cdiv(p.nH, p.TH);
+    if (2 * (TH + 1) > 256) return false;    // TMA box extent
     p.nGroups = cdiv(p.B, p.NB);
     p.nKB = cdiv(p.K, kBlockN);
     p.nC16 = p.C / 16;
-    p.xbytes = (uint32_t)((size_t)p.BW * p.BH * 16 * p.NB * 4);
+    p.BWY = (2 * p.TW + 3) & ~3;
+    p.xbytes1 = (uint32_t)((size_t)p.BW * 2 * TH * 16 * p.NB * 4);
+    p.xbytes2 = (uint32_t)((size_t)p.BW * (TH + 1) * 16 * p.NB * 4);
     const long long units = (long long)p.nGroups * p.nRB * p.nSeg * p.nKB;
     if (units > 0x7fffffffLL) return false;
     p.units = (int)units;
@@ -399,7 +516,7 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
 {
     if (!X || !prepared || !Y) return WG2X2_ERR_BAD_ARG;
     if (!fused_fwd_supported(B, H, W, C, K, WG2X2_NCHW)) return WG2X2_ERR_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 7u)) return WG2X2_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 15u)) return WG2X2_ERR_BAD_ARG;
     if ((out_scale == nullptr) != (out_shift == nullptr)) return WG2X2_ERR_BAD_ARG;
     FuParams p;
     p.Y = Y; p.out_scale = out_scale; p.out_shift = out_shift; p.residual = residual;
@@ -407,13 +524,21 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     if (!fused_geometry(p)) return WG2X2_ERR_UNSUPPORTED;
     EncodeTiledFn fn = encode_fn();
     if (!fn) return WG2X2_ERR_LAUNCH;
-    CUtensorMap mapX, mapW;
+    CUtensorMap mapX1, mapX2, mapW, mapY;
     {
         cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C, (cuuint64_t)B};
         cuuint64_t strides[3] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4, (cuuint64_t)C * H * W * 4};
-        cuuint32_t box[4] = {(cuuint32_t)p.BW, (cuuint32_t)p.BH, 16, (cuuint32_t)p.NB};
-        cuuint32_t estr[4] = {1, 1, 1, 1};
-        if (fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(X), dims, strides, box, estr,
+        // dense box: rows 2*th0 .. 2*th0 + 2*TH - 1
+        cuuint32_t box1[4] = {(cuuint32_t)p.BW, (cuuint32_t)(2 * p.TH), 16, (cuuint32_t)p.NB};
+        cuuint32_t estr1[4] = {1, 1, 1, 1};
+        if (fn(&mapX1, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(X), dims, strides, box1, estr1,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return WG2X2_ERR_LAUNCH;
+        // every second row: a box extent of 2*(TH+1) walked with stride 2 brings TH+1 rows
+        cuuint32_t box2[4] = {(cuuint32_t)p.BW, (cuuint32_t)(2 * (p.TH + 1)), 16, (cuuint32_t)p.NB};
+        cuuint32_t estr2[4] = {1, 2, 1, 1};
+        if (fn(&mapX2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(X), dims, strides, box2, estr2,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return WG2X2_ERR_LAUNCH;
@@ -421,10 +546,21 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     {
         cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)K, 16};
         cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)K * C * 4};
-        cuuint32_t box[3] = {16, (cuuint32_t)kBlockN, 1};
+        cuuint32_t box[3] = {16, (cuuint32_t)kBlockN, 4};
         cuuint32_t estr[3] = {1, 1, 1};
         if (fn(&mapW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(prepared), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return WG2X2_ERR_LAUNCH;
+    }
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)K, (cuuint64_t)B};
+        cuuint64_t strides[3] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4, (cuuint64_t)K * H * W * 4};
+        // output rows of one parity: a box extent of 2*TH walked with stride 2 is TH rows
+        cuuint32_t box[4] = {(cuuint32_t)p.BWY, (cuuint32_t)(2 * p.TH), 16, (cuuint32_t)p.NB};
+        cuuint32_t estr[4] = {1, 2, 1, 1};
+        if (fn(&mapY, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, Y, dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return WG2X2_ERR_LAUNCH;
     }
@@ -435,11 +571,11 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     if (extras) {
         if (cudaFuncSetAttribute(layer_fwd_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess)
             return WG2X2_ERR_LAUNCH;
-        layer_fwd_fused_kernel<true><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX, mapW, p);
+        layer_fwd_fused_kernel<true><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
     } else {
         if (cudaFuncSetAttribute(layer_fwd_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess)
             return WG2X2_ERR_LAUNCH;
-        layer_fwd_fused_kernel<false><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX, mapW, p);
+        layer_fwd_fused_kernel<false><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
     }
     return launch_status();
 }
