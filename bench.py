@@ -335,7 +335,10 @@ def main():
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
     ap.add_argument("--e2e-chunks", type=int, default=2, help="chunks of the host-buffer pipeline")
-    ap.add_argument("--fused", action="store_true", help="time the one-kernel layer (X -> Y, V never stored) instead of the two kernels")
+    ap.add_argument("--path", default="auto", choices=["auto", "fused", "two-kernel"],
+                    help="layer forward: the one-kernel path (X -> Y, V never stored), the two kernels, or (auto) whichever "
+                         "wg2x2_layer_fwd_prepared picks for the shape")
+    ap.add_argument("--fused", action="store_true", help="same as --path fused")
     ap.add_argument("--net-layout", default="NHWC", choices=["NHWC", "NCHW"], help="cfg4: physical layout of the activations")
     ap.add_argument("--no-graph", action="store_true", help="cfg4: launch the network eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -403,7 +406,10 @@ def main():
         else:
             wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
 
-    use_fused = args.fused and prepared is not None and args.layout == "NCHW" and wg2x2.fused_supported(B, H, W, C, K, "NCHW")
+    path = "fused" if args.fused else args.path
+    fused_ok = prepared is not None and args.layout == "NCHW" and wg2x2.fused_supported(B, H, W, C, K, "NCHW")
+    fused_pays = K <= 128 or (K <= 256 and C <= 64)          # the library's own rule (wg2x2_layer_fwd_prepared)
+    use_fused = fused_ok and (path == "fused" or (path == "auto" and fused_pays))
 
     def step(i):
         if use_fused:
@@ -499,7 +505,10 @@ def main():
         fb = bytesX + bytesW + bytesY
         roof = dict(kernel="layer_fwd_fused (transform + ReLU + products + output transform, one kernel)", bound="hbm",
                     achieved=fb / (ms_k2 * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"],
-                    note="strict layer bound: only X, W and Y cross HBM; the on-SM transform is bound by instruction issue")
+                    note="only X, W and Y cross HBM (%.1f MB); the kernel is paced by the SM, not by HBM: per 128 tiles x 64 channels x "
+                         "64 output channels it issues 288 tcgen05.mma (N=64, K=8; the output transform is folded into 36 signed MMAs per 8 "
+                         "channels instead of 16) and its transform warps compute 16 x 128 x 64 values" % (fb / 1e6),
+                    tensor_tflops_algorithmic=flops / (ms_k2 * 1e-3) / 1e12, tensor_tflops_issued=2.25 * flops / (ms_k2 * 1e-3) / 1e12)
     elif ms_k2 >= ms_k1:
         if args.math == "tf32" and k2_t_tensor > k2_t_hbm:
             roof = dict(kernel="conv_fwd (products + output transform)", bound="tensor", achieved=flops / (ms_k2 * 1e-3) / 1e12,
@@ -515,29 +524,31 @@ def main():
     # under profiles/ (taken at this workload's full size); None for shapes that were not captured
     measured_traffic = {("cfg2", 64, "NCHW", "imtrans"): 197.8e6, ("cfg2", 64, "NCHW", "conv"): 224.7e6}
     roof["traffic"] = None if use_fused else measured_traffic.get((args.workload, B, args.layout, "conv" if roof["kernel"].startswith("conv") else "imtrans"))
-    roof["kernels_ms"] = {"imtrans_fwd": ms_k1, "conv_fwd": ms_k2}
-    roof["imtrans_fwd_gbs"] = k1_bytes / (ms_k1 * 1e-3) / 1e9
-    roof["conv_fwd_gbs"] = k2_bytes / (ms_k2 * 1e-3) / 1e9
-    roof["conv_fwd_tflops"] = flops / (ms_k2 * 1e-3) / 1e12
+    if use_fused:
+        roof["kernels_ms"] = {"layer_fwd_fused": ms_k2}
+    else:
+        roof["kernels_ms"] = {"imtrans_fwd": ms_k1, "conv_fwd": ms_k2}
+        roof["imtrans_fwd_gbs"] = k1_bytes / (ms_k1 * 1e-3) / 1e9
+        roof["conv_fwd_gbs"] = k2_bytes / (ms_k2 * 1e-3) / 1e9
+        roof["conv_fwd_tflops"] = flops / (ms_k2 * 1e-3) / 1e12
 
     out = {
         "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
         "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
-                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((k1_bytes + k2_bytes) / 1e6),
+                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((bytesX + bytesW + bytesY if use_fused else k1_bytes + k2_bytes) / 1e6),
                    "weights": "prepared once outside the timed region (wg2x2_weights_prepare)",
                    "e2e": "wg2x2.HostLayerPipeline.submit: pinned host X -> pinned host Y every step, %d chunks, H2D / kernels / D2H on three "
                           "streams, consecutive steps overlapped (two host output buffers)" % args.e2e_chunks},
-        "layer_gbs_two_kernel": (k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
+        "layer_gbs": (bytesX + bytesW + bytesY if use_fused else k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
         "layer_tflops": flops * world / (ms_step * 1e-3) / 1e12,
         "roofline": roof, "clocks": clocks,
         "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": bytesX, "d2h_bytes_per_step": bytesY,
                 "ms_per_step": e2e_ms},
         "gpu_launches": args.steps * (1 if use_fused else 2),
     }
-    if use_fused:
-        out["config"]["path"] = "one fused kernel"
+    out["config"]["path"] = "one fused kernel (wg2x2_layer_fwd_prepared's choice for this shape)" if use_fused else "two kernels, V through HBM"
     if not args.no_cpu_baseline:
         cb, _, _ = cpu_oracle_rate(wl, args.layout)
         out["cpu_baseline"] = cb

@@ -302,6 +302,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int bi = le / per_img, rem = le - bi * per_img;   // their A rows feed TMEM lanes nobody reads
         const int thl = rem / prm.TW, twl = rem - thl * prm.TW;
         const int BW = prm.BW;
+        const bool need_l = (lane == 0) || (twl == 0), need_r = (lane == 31) || (twl == prm.TW - 1);
         const float lo = prm.relu ? 0.f : -__int_as_float(0x7f800000);
         const int spu = 4 * nC16;                               // steps per unit
         const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -333,13 +334,17 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 float o[4][4];   // [j][channel within the quad]
 #pragma unroll
                 for (int cq = 0; cq < 4; ++cq) {
-                    // the tile's 4 pixels of rows a and b: the middle two as one 8-byte load, the outer two alone
+                    // row i of B^T d at the tile's 4 pixels: the middle two from one 8-byte load per input row; the outer
+                    // two are the neighbouring tiles' middle values (warp shuffle), except at the ends of a tile row or of
+                    // the warp, where they are loaded
                     const float *pa = xq + (c4 * 4 + cq) * chs;
                     const float *pb = pa + dab;
                     const float2 am = *reinterpret_cast<const float2 *>(pa + 1);
                     const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
-                    const float a0 = pa[0], a3 = pa[3], b0 = pb[0], b3 = pb[3];
-                    const float r0 = fmaf(sb, b0, a0), r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y), r3 = fmaf(sb, b3, a3);
+                    const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
+                    float r0 = __shfl_up_sync(0xffffffffu, r2, 1), r3 = __shfl_down_sync(0xffffffffu, r1, 1);
+                    if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
+                    if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
                     // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
                     o[0][cq] = fmaxf(r0 - r2, lo);
                     o[1][cq] = fmaxf(r1 + r2, lo);
