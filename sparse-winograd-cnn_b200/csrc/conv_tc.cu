@@ -38,6 +38,7 @@ constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kC
 constexpr long long kSpinLimit = 40LL * 1000 * 1000;  // try_wait polls before a wait gives up (~ a second)
 
 __device__ unsigned int g_tc_status[2];  // [0] = 0 ok / 1 timeout, [1] = where (role<<8 | detail)
+__device__ unsigned int g_tc_diag[32];   // after a timeout: per role (where >> 8), the wait it was in when it gave up or was told to
 
 #ifdef WG_TC_TRACE   // development aid: cycle stamps of CTA 0's roles, read back by wg2x2_debug_read_trace
 __device__ long long g_tc_trace[4096];
@@ -78,12 +79,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 {
     for (long long it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 1023) == 1023 && *abort_flag) return false;
+        if ((it & 1023) == 1023 && *abort_flag) { g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x40000000u; return false; }
     }
     *abort_flag = 1;
+    g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x80000000u;
     g_tc_status[1] = where;
     g_tc_status[0] = 1;
     return false;
+}
+
+// The same wait for a role in which all 32 lanes of a warp poll: lanes can leave the polling loop in different
+// iterations, and what follows (tcgen05.ld / tcgen05.st / tcgen05.wait) is .sync.aligned, which a diverged
+// warp must not execute.  The vote brings the lanes back together and makes the outcome (and so every
+// break out of the role's loop) the same for all of them.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where)
+{
+    const bool ok = mbar_wait(bar, parity, abort_flag, where);
+    return __all_sync(0xffffffffu, ok);
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
@@ -353,7 +365,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int buf = i & 1;
-                if (ok && !mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
+                if (ok && !mbar_wait_warp(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
                 acc_use[buf]++;
                 if (ok) {
                     if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * tr);
@@ -664,6 +676,13 @@ void dw_reduce_launch(const float *partial, const float *mask, float *dW, long l
 #include "conv_tc_bwd.cuh"
 #include "conv_tc_fused.cuh"
 
+#if defined(WG_TC_TRACE) || defined(WG_TC_DIAG)   // development builds only
+extern "C" int wg2x2_debug_read_diag(unsigned int *host)
+{
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(host, g_tc_diag, sizeof(unsigned int) * 32) == cudaSuccess ? 0 : -1;
+}
+#endif
 #ifdef WG_TC_TRACE
 extern "C" int wg2x2_debug_read_trace(long long *host, int n)
 {

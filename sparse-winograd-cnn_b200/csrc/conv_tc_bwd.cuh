@@ -336,7 +336,7 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                     if (vec && use_mask && off[rr] >= 0) mk[rr] = __ldg(reinterpret_cast<const float4 *>(prm.mask + off[rr] + 4 * (lane & 7)));
                 }
                 if (cc == 0) {   // first chunk of the unit: only now wait for the accumulator
-                    if (!mbar_wait(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x800u | (ew << 4) | buf)) { ok = false; break; }
+                    if (!mbar_wait_warp(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x800u | (ew << 4) | buf)) { ok = false; break; }
                     acc_use[buf]++;
                     tc_fence_after();
                 }

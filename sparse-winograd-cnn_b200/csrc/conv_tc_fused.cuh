@@ -55,6 +55,7 @@ struct FuParams {
     const float *out_scale, *out_shift, *residual;
     int B, H, W, C, K, nH, nW, outH, outW;
     int TH, TW, NB, BW, BWY;         // block of tiles; BW = width of the input box, BWY = of the output box
+    int lp_log2;                     // a tile row takes 2^lp_log2 >= TW TMEM lanes
     int nRB, nSeg, nGroups, nKB, nC16;
     int units, relu;
     uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows) and of the row-stride-2 (TH+1 rows) box
@@ -74,9 +75,10 @@ __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, 
     for (long long it = 0; it < kSpinLimit / 8; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(ns);
-        if ((it & 255) == 255 && *abort_flag) return false;
+        if ((it & 255) == 255 && *abort_flag) { g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x40000000u; return false; }
     }
     *abort_flag = 1;
+    g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x80000000u;
     g_tc_status[1] = where;
     g_tc_status[0] = 1;
     return false;
@@ -153,9 +155,12 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     const float *xgen = reinterpret_cast<const float *>(gen_base + kXOff);
     uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
     // barriers: full[G] (A group written by a team + its W tiles landed), free[G] (the four issuers' MMAs on the
-    // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[XB], xempty[XB], ywritten[2], yfree[2]
+    // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[2*XB], xempty[XB], ywritten[2], yfree[2].
+    // Step n fills X buffer n % XB but signals xfull[n % (2*XB)]: with an odd XB the two teams take turns on a
+    // buffer, and a parity wait can only tell a barrier's current phase from the one before it, so a waiter has
+    // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
     constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
-                  kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXbufs, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
+                  kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + 2 * kFuXbufs, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
     static_assert((kB8 + 2) * 8 <= kCtrlBytes, "control block");
     auto full_bar = [&](int g) { return bars + 8u * (kB0 + g); };
     auto free_bar = [&](int g) { return bars + 8u * (kB1 + g); };
@@ -173,7 +178,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     if (threadIdx.x == 0) {
         for (int g = 0; g < kFuAGroups; ++g) { mbar_init(full_bar(g), kFuTeamWarps + 1); mbar_init(free_bar(g), 4); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 2); mbar_init(acce_bar(b), kEpiWarps); }
-        for (int b = 0; b < kFuXbufs; ++b) { mbar_init(xfull_bar(b), 1); mbar_init(xempty_bar(b), kFuTeamWarps); }
+        for (int b = 0; b < 2 * kFuXbufs; ++b) mbar_init(xfull_bar(b), 1);
+        for (int b = 0; b < kFuXbufs; ++b) mbar_init(xempty_bar(b), kFuTeamWarps);
         for (int h = 0; h < 2; ++h) { mbar_init(ywritten_bar(h), 4); mbar_init(yfree_bar(h), 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -220,10 +226,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             bool ready = total > 0 && mbar_try_wait(full_bar(0), 0);
             for (int n = 0; n < total; ++n) {
                 if (warp == 0) TC_TRACE(1024 + 5 * trm);
-                if (!ready && !mbar_wait(full_bar(g), gph, abort_flag, 0x300u | g)) break;
+                if (!ready && !mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g)) break;
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 1);
                 // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
-                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x200u | warp)) break;
+                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a)) break;
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 2);
                 tc_fence_after();
                 int g2 = g + 1; uint32_t gph2 = gph;
@@ -240,7 +246,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     }
                 }
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 3);
-                umma_commit(free_bar(g));
+                // (an issuer that added nothing in this slot has nothing for a commit to track: it arrives directly)
+                if (i >= a && i <= a + 2) umma_commit(free_bar(g)); else mbar_arrive(free_bar(g));
                 if (cc == nC16 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
                 if (warp == 0) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
                 g = g2; gph = gph2;
@@ -248,7 +255,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             }
         } else if (warp == 4 && lane == 0) {
             // ------------------------------ X producer -----------------------------------
-            int xb = 0; uint32_t xph = 0;
+            int xb = 0, xj = 0; uint32_t xph = 0;               // buffer n % XB (xempty phase parity xph), barrier xfull[n % (2*XB)]
             bool ok = true;
             int trx = 0; (void)trx;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
@@ -263,9 +270,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     for (int cc = 0; cc < nC16; ++cc) {
                         if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100)) { ok = false; break; }
                         TC_TRACE(trx); ++trx;
-                        mbar_expect_tx(xfull_bar(xb), bytes);
-                        tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xb), x0, h_lo, cc * 16, b0);
+                        mbar_expect_tx(xfull_bar(xj), bytes);
+                        tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xj), x0, h_lo, cc * 16, b0);
                         if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
+                        if (++xj == 2 * kFuXbufs) xj = 0;
                     }
                 }
             }
@@ -296,19 +304,25 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int tw8 = (warp - 16) % kFuTeamWarps;
         const int l = (tw8 & 3) * 32 + lane;                   // tile = TMEM lane = A-tile row
         const int hq = tw8 >> 2;                               // which 8 of the step's 16 channels
-        const int per_img = prm.TH * prm.TW;
-        const bool live = l < prm.NB * per_img;
-        const int le = live ? l : 0;                            // dead lanes (block smaller than 128 tiles) shadow tile 0:
-        const int bi = le / per_img, rem = le - bi * per_img;   // their A rows feed TMEM lanes nobody reads
-        const int thl = rem / prm.TW, twl = rem - thl * prm.TW;
+        // a tile row occupies LP = 2^lp_log2 >= TW consecutive lanes, so it never straddles a warp (or, for
+        // LP <= 16, a half-warp: the 8-byte loads of a half-warp then stay conflict-free)
+        const int trow = l >> prm.lp_log2, tcol = l & ((1 << prm.lp_log2) - 1);
+        const bool live = tcol < prm.TW && trow < prm.NB * prm.TH;
+        const int LP = 1 << prm.lp_log2;
+        const int row_e = live ? trow : 0, twl = live ? tcol : 0;   // dead lanes shadow tile 0: their A rows feed TMEM lanes nobody reads
+        const int bi = row_e / prm.TH, thl = row_e - bi * prm.TH;
         const int BW = prm.BW;
-        const bool need_l = (lane == 0) || (twl == 0), need_r = (lane == 31) || (twl == prm.TW - 1);
+        // the outer pixels of a tile's window come from the neighbouring lanes, except at the ends of a tile row
+        const int src_l = (lane & ~(LP - 1)) | ((tcol + LP - 1) & (LP - 1)), src_r = (lane & ~(LP - 1)) | ((tcol + 1) & (LP - 1));
+        const bool need_l = (tcol == 0), need_r = (tcol == prm.TW - 1) || (tcol == LP - 1);
         const float lo = prm.relu ? 0.f : -__int_as_float(0x7f800000);
         const int spu = 4 * nC16;                               // steps per unit
         const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total = my_units * spu;
-        // step n uses X buffer n % kFuXbufs and A group n % kFuAGroups; this team takes n = team, team + 2, ...
-        int xb = team % kFuXbufs, g = team % kFuAGroups, r = team;
+        // step n uses X buffer n % kFuXbufs (barrier xfull[n % (2*kFuXbufs)]) and A group n % kFuAGroups; this team
+        // takes n = team, team + 2, ...
+        static_assert(kFuXbufs >= 2 && kFuAGroups % 2 == 0, "each xfull barrier and each A group belongs to one team");
+        int xj = team, g = team % kFuAGroups, r = team;
         uint32_t xph = 0, gph = 0;
         bool ok = true;
         int trt = 0; (void)trt;
@@ -320,9 +334,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
             const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
-            if (!mbar_wait(xfull_bar(xb), xph, abort_flag, 0xB00u | xb)) { ok = false; break; }
+            const int xb = xj < kFuXbufs ? xj : xj - kFuXbufs;
+            if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            if (!mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
+            if (!mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
             const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
@@ -339,10 +354,20 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     // the warp, where they are loaded
                     const float *pa = xq + (c4 * 4 + cq) * chs;
                     const float *pb = pa + dab;
+#ifdef WG_TC_TRACE   // development build: bounds of the two 8-byte loads, recorded instead of faulting
+                    {
+                        const long long oa = (pa + 1) - xgen, ob = (pb + 1) - xgen;
+                        if (oa < 0 || ob < 0 || oa + 1 >= kFuXbufs * (kFuXbufBytes / 4) || ob + 1 >= kFuXbufs * (kFuXbufBytes / 4) || (oa & 1) || (ob & 1)) {
+                            g_tc_status[1] = 0xEE000000u | (unsigned)(oa & 0xFFFFFF);
+                            g_tc_status[0] = 2;
+                            continue;
+                        }
+                    }
+#endif
                     const float2 am = *reinterpret_cast<const float2 *>(pa + 1);
                     const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
                     const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
-                    float r0 = __shfl_up_sync(0xffffffffu, r2, 1), r3 = __shfl_down_sync(0xffffffffu, r1, 1);
+                    float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
                     if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
                     if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
                     // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
@@ -367,7 +392,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 mbar_arrive(xempty_bar(xb));
             }
             r += 2; if (r >= spu) r -= spu;
-            xb += 2; if (xb >= kFuXbufs) { xb -= kFuXbufs; xph ^= 1u; }
+            xj += 2; if (xj >= 2 * kFuXbufs) { xj -= 2 * kFuXbufs; xph ^= 1u; }
             g += 2; if (g >= kFuAGroups) { g -= kFuAGroups; gph ^= 1u; }
         }
         (void)ok;
@@ -377,11 +402,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int q = warp & 3;
         const int half = ew >> 2;                                // which 32 of the 64 output channels
         const int l = q * 32 + lane;
-        const int per_img = prm.TH * prm.TW;
-        const bool live = l < prm.NB * per_img;
-        const int le = live ? l : 0;
-        const int bi = le / per_img, rem = le - bi * per_img;
-        const int thl = rem / prm.TW, twl = rem - thl * prm.TW;
+        const int trow = l >> prm.lp_log2, tcol = l & ((1 << prm.lp_log2) - 1);   // same lane <-> tile map as the transform warps
+        const bool live = tcol < prm.TW && trow < prm.NB * prm.TH;
+        const int row_e = live ? trow : 0, twl = live ? tcol : 0;
+        const int bi = row_e / prm.TH, thl = row_e - bi * prm.TH;
         const int BWY = prm.BWY, TH = prm.TH;
         const int box_floats = prm.NB * 16 * TH * BWY;           // one staged box
         float *stage0 = reinterpret_cast<float *>(gen_base + kYOff + half * kFuYStageBytes);
@@ -398,7 +422,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
                 if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a);
-                if (!mbar_wait_sleepy(accf_bar(a), units_done & 1u, abort_flag, 0x400u | (ew << 4) | a, 400)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_sleepy(accf_bar(a), units_done & 1u, abort_flag, 0x400u | (ew << 4) | a, 400))) { ok = false; break; }
                 if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a + 1);
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 2 * kBlockN + half * 32);
@@ -420,7 +444,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                         mbar_arrive(yfree_bar(half));
                     }
-                    if (!mbar_wait(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
+                    if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
                     float *stage = stage0 + (st_use & 1u) * box_floats;
                     if (live) {
                         const int h = 2 * th + a;
@@ -445,13 +469,16 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) mbar_arrive(ywritten_bar(half));
+                    bool stored = true;
                     if (elected) {
-                        if (!mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew)) { ok = false; break; }
-                        if (kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
+                        stored = mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew);
+                        if (stored && kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
                             tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
+                    // the warp goes on together (tcgen05.ld is next) and with one verdict
+                    if (!__all_sync(0xffffffffu, stored)) { ok = false; break; }
                     ++st_use;
                 }
                 if (!ok) break;
@@ -462,9 +489,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
+    __syncwarp();                        // the lanes of a warp took different roles: together again before the aligned instructions
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -489,7 +518,10 @@ static bool fused_geometry(FuParams &p)
     p.BW = (2 * p.TW + 5 + 3) & ~3;
     // the larger of the two boxes (2*TH rows x BW x 16 channels x NB images) has to fit an X buffer
     auto box_bytes = [&](int th, int nb) { return (size_t)p.BW * 2 * th * 16 * 4 * nb; };
-    int TH = kBlockM / p.TW;
+    p.lp_log2 = 0;
+    while ((1 << p.lp_log2) < p.TW) ++p.lp_log2;
+    const int max_rows = kBlockM >> p.lp_log2;              // tile rows (of all images) per unit
+    int TH = max_rows;
     if (TH > p.nH) TH = p.nH;
     while (TH > 1 && box_bytes(TH, 1) > (size_t)kFuXbufBytes) --TH;
     if (box_bytes(TH, 1) > (size_t)kFuXbufBytes) return false;
@@ -498,7 +530,7 @@ static bool fused_geometry(FuParams &p)
     p.TH = TH;
     p.NB = 1;
     if (TH == p.nH) {
-        int nb = kBlockM / (TH * p.TW);
+        int nb = max_rows / TH;
         while (nb > 1 && box_bytes(TH, nb) > (size_t)kFuXbufBytes) --nb;
         if (nb > p.B) nb = p.B;
         p.NB = nb < 1 ? 1 : nb;

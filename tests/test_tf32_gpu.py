@@ -214,6 +214,35 @@ def test_fused_layer_forward(wg, oracle, shape):
     _status_ok(wg)
 
 
+@pytest.mark.parametrize("shape,launches", [((256, 56, 56, 64, 64), 1500), ((40, 28, 28, 128, 128), 1500)])
+def test_fused_many_units_per_cta_repeated(wg, oracle, shape, launches):
+    """Many units per CTA, many launches: every launch on the same input must give the same bits, the device
+    status must stay clean, and a sample of the result must match the oracle.  (The rings inside the kernel wrap
+    around many times per launch here; a lost or mis-attributed barrier phase shows up as a changed result, a
+    time-out status or a failed launch.)"""
+    import torch
+    B, H, W, C, K = shape
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    Xs = [torch.randn((B, C, H, W), generator=gen, device="cuda") for _ in range(3)]
+    Wt = 0.05 * torch.randn((16, C, K), generator=gen, device="cuda")
+    prepared = wg.prepare_weights(Wt)
+    Y = torch.empty((B, K, H, W), device="cuda")
+    first = [None] * 3
+    for it in range(launches):
+        wg.layer_fwd_fused(Xs[it % 3], prepared, K, relu=True, out=Y)
+        if it < 3 or it % 250 < 3 or it >= launches - 3:
+            if first[it % 3] is None:
+                first[it % 3] = Y.clone()
+            else:
+                assert torch.equal(Y, first[it % 3]), "launch %d differs from the first launch on the same input" % it
+    _status_ok(wg)
+    # two images of the first input against the float64 oracle
+    xs = np.ascontiguousarray(np.transpose(Xs[0][:2].cpu().numpy(), (0, 2, 3, 1)))
+    want = oracle.conv_fwd(oracle.imtrans_fwd(xs, relu=True), Wt.cpu().numpy(), H, W)
+    got = np.transpose(first[0][:2].cpu().numpy(), (0, 2, 3, 1))
+    assert oracle.max_rel(got, want) <= TOL_TF32
+
+
 def test_layer_fwd_prepared_falls_back_to_two_kernels(wg, oracle):
     shape = (2, 7, 7, 36, 20)        # odd width: not a fused shape
     B, H, W, C, K = shape
