@@ -31,17 +31,20 @@
 // it (from L2 after the first time); HBM sees X once and Y once.
 #pragma once
 
-constexpr int kFuAGroups = 4;                      // ring of A groups in tensor memory; a group = four [128 x 16] tiles
+constexpr int kFuAGroups = 2;                      // ring of A groups in tensor memory; a group = four [128 x 32] tiles
+constexpr int kFuGroupCols = 4 * 32;               // tensor-memory columns of an A group
 constexpr int kFuACol0 = 4 * kBlockN;              // first tensor-memory column of the A ring
 constexpr int kFuWStages = kFuAGroups;            // a W stage travels with its A group: one "slot" of the ring
-constexpr int kFuWBytes = 4 * 64 * 64;             // four (one per j) [64 out-channels][16 channels] tiles
+constexpr int kFuWTile = 64 * 128;                 // one [64 out-channels][32 channels] tile, rows of 128 bytes
+constexpr int kFuWBytes = 4 * kFuWTile;            // four of them, one per Winograd column j
 constexpr int kFuXbufs = 3;
+constexpr int kFuXfull = 4 * kFuXbufs;             // full-barriers of the X ring (see the kernel)
 constexpr int kFuXbufBytes = 32768;
 constexpr int kFuTeamWarps = 8;                    // transform warps per team: one thread = one tile x 8 channels
 constexpr int kFuThreads = 256 + 256 + 2 * 32 * kFuTeamWarps;   // 2 control WGs, 2 epilogue WGs, 2 transform teams (2 WGs each)
 constexpr int kFuYStageBytes = kFuXbufBytes;      // per epilogue warpgroup: two [NB][16 channels][TH rows][2*TW pixels] boxes of Y
 constexpr int kFuSmemBytes = kFuWStages * kFuWBytes + kFuXbufs * kFuXbufBytes + 2 * kFuYStageBytes + kCtrlBytes + 1024;
-static_assert(kFuACol0 + kFuAGroups * 64 <= (int)kTmemCols, "tensor memory columns");
+static_assert(kFuACol0 + kFuAGroups * kFuGroupCols <= (int)kTmemCols, "tensor memory columns");
 static_assert(kFuSmemBytes <= 232448, "shared memory per CTA");
 // Register hand-over (setmaxnreg): the kernel starts with 64 registers per thread; the increase of the transform
 // warps can only be served from what the other warps of the same CTA have given back, and it blocks (for
@@ -56,7 +59,7 @@ struct FuParams {
     int B, H, W, C, K, nH, nW, outH, outW;
     int TH, TW, NB, BW, BWY;         // block of tiles; BW = width of the input box, BWY = of the output box
     int lp_log2;                     // a tile row takes 2^lp_log2 >= TW TMEM lanes
-    int nRB, nSeg, nGroups, nKB, nC16;
+    int nRB, nSeg, nGroups, nKB, nC32;        // nC32 = ring slots (32 input channels each) per Winograd row
     int units, relu;
     uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows) and of the row-stride-2 (TH+1 rows) box
 };
@@ -156,11 +159,12 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
     // barriers: full[G] (A group written by a team + its W tiles landed), free[G] (the four issuers' MMAs on the
     // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[2*XB], xempty[XB], ywritten[2], yfree[2].
-    // Step n fills X buffer n % XB but signals xfull[n % (2*XB)]: with an odd XB the two teams take turns on a
-    // buffer, and a parity wait can only tell a barrier's current phase from the one before it, so a waiter has
-    // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
+    // A step is 16 input channels; two consecutive steps (taken by the same team) fill one 32-channel slot.
+    // Step n fills X buffer n % XB but signals xfull[n % (4*XB)]: the two teams take turns on a buffer, and a
+    // parity wait can only tell a barrier's current phase from the one before it, so a waiter has to see every
+    // phase of the barrier it waits on; with teams changing every two steps xfull[j] is always the same team's.
     constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
-                  kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + 2 * kFuXbufs, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
+                  kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXfull, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
     static_assert((kB8 + 2) * 8 <= kCtrlBytes, "control block");
     auto full_bar = [&](int g) { return bars + 8u * (kB0 + g); };
     auto free_bar = [&](int g) { return bars + 8u * (kB1 + g); };
@@ -176,9 +180,9 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int g = 0; g < kFuAGroups; ++g) { mbar_init(full_bar(g), kFuTeamWarps + 1); mbar_init(free_bar(g), 4); }
+        for (int g = 0; g < kFuAGroups; ++g) { mbar_init(full_bar(g), 2 * kFuTeamWarps + 1); mbar_init(free_bar(g), 4); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 2); mbar_init(acce_bar(b), kEpiWarps); }
-        for (int b = 0; b < 2 * kFuXbufs; ++b) mbar_init(xfull_bar(b), 1);
+        for (int b = 0; b < kFuXfull; ++b) mbar_init(xfull_bar(b), 1);
         for (int b = 0; b < kFuXbufs; ++b) mbar_init(xempty_bar(b), kFuTeamWarps);
         for (int h = 0; h < 2; ++h) { mbar_init(ywritten_bar(h), 4); mbar_init(yfree_bar(h), 1); }
         *abort_flag = 0;
@@ -193,7 +197,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
 
-    const int nC16 = prm.nC16;
+    const int nC32 = prm.nC32;
     auto decode = [&](int u, int &g, int &rb, int &seg, int &kb) {
         kb = u % prm.nKB; u /= prm.nKB;
         seg = u % prm.nSeg; u /= prm.nSeg;
@@ -213,11 +217,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             constexpr uint32_t idesc_neg = idesc_pos | (1u << 14);            // negate B
             const int a = warp >> 1, e = warp & 1;
             const uint32_t d_tmem = tmem_base + (uint32_t)(warp * kBlockN);
-            const uint32_t a_tmem0 = tmem_base + (uint32_t)(kFuACol0 + e * 16);
-            const uint64_t bdesc0 = make_desc_k_sw64(wbase + e * (kFuWBytes / 4));
+            const uint32_t a_tmem0 = tmem_base + (uint32_t)(kFuACol0 + e * 32);
+            const uint64_t bdesc0 = make_desc_k_sw128(wbase + e * kFuWTile);
             const uint32_t b_hi = (uint32_t)(bdesc0 >> 32), b_lo0 = (uint32_t)bdesc0;
             const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-            const int total = my_units * 4 * nC16;
+            const int total = my_units * 4 * nC32;
             int g = 0; uint32_t gph = 0;
             int i = 0, cc = 0;
             uint32_t units_done = 0;
@@ -237,25 +241,27 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 ready = (n + 1 < total) && mbar_try_wait(full_bar(g2), gph2);
                 if (i >= a && i <= a + 2) {
                     const bool neg_a = (a == 1 && i >= 2);
-                    const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * 64), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
+                    const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
 #pragma unroll
                     for (int jj = 0; jj < 3; ++jj) {
                         const bool neg_e = (e == 1 && jj >= 1);                      // At[1][j] = -1 for j = 2, 3
-                        umma_tf32_ts_x2(d_tmem, a_tmem + (uint32_t)(jj * 16), b_lo + (uint32_t)(jj * (kFuWBytes / 4 >> 4)), b_hi,
-                                        (neg_a != neg_e) ? idesc_neg : idesc_pos, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
+                        const uint32_t idesc = (neg_a != neg_e) ? idesc_neg : idesc_pos;
+                        const uint32_t aj = a_tmem + (uint32_t)(jj * 32), bj = b_lo + (uint32_t)(jj * (kFuWTile >> 4));
+                        umma_tf32_ts_x2(d_tmem, aj, bj, b_hi, idesc, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
+                        umma_tf32_ts_x2(d_tmem, aj + 16u, bj + 4u, b_hi, idesc, 1u);
                     }
                 }
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 3);
                 // (an issuer that added nothing in this slot has nothing for a commit to track: it arrives directly)
                 if (i >= a && i <= a + 2) umma_commit(free_bar(g)); else mbar_arrive(free_bar(g));
-                if (cc == nC16 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
+                if (cc == nC32 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
                 if (warp == 0) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
                 g = g2; gph = gph2;
-                if (++cc == nC16) { cc = 0; if (++i == 4) { i = 0; ++units_done; } }
+                if (++cc == nC32) { cc = 0; if (++i == 4) { i = 0; ++units_done; } }
             }
         } else if (warp == 4 && lane == 0) {
             // ------------------------------ X producer -----------------------------------
-            int xb = 0, xj = 0; uint32_t xph = 0;               // buffer n % XB (xempty phase parity xph), barrier xfull[n % (2*XB)]
+            int xb = 0, xj = 0; uint32_t xph = 0;               // buffer n % XB (xempty phase parity xph), barrier xfull[n % (4*XB)]
             bool ok = true;
             int trx = 0; (void)trx;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
@@ -267,13 +273,13 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     const int h_lo = 2 * th0 - (i == 0 ? 1 : 0);
                     const CUtensorMap *map = strided ? &mapX2 : &mapX1;
                     const uint32_t bytes = strided ? prm.xbytes2 : prm.xbytes1;
-                    for (int cc = 0; cc < nC16; ++cc) {
+                    for (int cc = 0; cc < 2 * nC32; ++cc) {     // channels beyond C arrive as zeros
                         if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100)) { ok = false; break; }
                         TC_TRACE(trx); ++trx;
                         mbar_expect_tx(xfull_bar(xj), bytes);
                         tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xj), x0, h_lo, cc * 16, b0);
                         if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
-                        if (++xj == 2 * kFuXbufs) xj = 0;
+                        if (++xj == kFuXfull) xj = 0;
                     }
                 }
             }
@@ -287,10 +293,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 int g, rb, seg, kb;
                 decode(u, g, rb, seg, kb);
                 for (int i = 0; i < 4 && ok; ++i)
-                    for (int cc = 0; cc < nC16; ++cc) {
+                    for (int cc = 0; cc < nC32; ++cc) {
                         if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100)) { ok = false; break; }
                         mbar_expect_tx(full_bar(s), kFuWBytes);
-                        tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), cc * 16, kb * kBlockN, 4 * i);
+                        tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), cc * 32, kb * kBlockN, 4 * i);
                         if (++s == kFuWStages) { s = 0; ph ^= 1u; }
                     }
             }
@@ -308,50 +314,60 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         // LP <= 16, a half-warp: the 8-byte loads of a half-warp then stay conflict-free)
         const int trow = l >> prm.lp_log2, tcol = l & ((1 << prm.lp_log2) - 1);
         const bool live = tcol < prm.TW && trow < prm.NB * prm.TH;
+        // The outer two pixels of a tile's window are the neighbouring tiles' middle ones and come by a rotation
+        // among the lanes of the tile row.  Dead lanes (their A rows feed TMEM lanes nobody reads) work for their
+        // neighbours: with at least two of them per tile row, the first reads the pixel pair right of the last tile
+        // and the last one the pair left of the first tile; otherwise the lanes at the ends load their outer pixel.
+        // Rows beyond the block shadow row 0.
         const int LP = 1 << prm.lp_log2;
-        const int row_e = live ? trow : 0, twl = live ? tcol : 0;   // dead lanes shadow tile 0: their A rows feed TMEM lanes nobody reads
+        const bool halo_by_lanes = LP - prm.TW >= 2;
+        const int row_e = trow < prm.NB * prm.TH ? trow : 0;
+        const int twl = halo_by_lanes ? ((tcol == LP - 1) ? -1 : (tcol < prm.TW ? tcol : prm.TW)) : (live ? tcol : 0);
         const int bi = row_e / prm.TH, thl = row_e - bi * prm.TH;
         const int BW = prm.BW;
-        // the outer pixels of a tile's window come from the neighbouring lanes, except at the ends of a tile row
         const int src_l = (lane & ~(LP - 1)) | ((tcol + LP - 1) & (LP - 1)), src_r = (lane & ~(LP - 1)) | ((tcol + 1) & (LP - 1));
-        const bool need_l = (tcol == 0), need_r = (tcol == prm.TW - 1) || (tcol == LP - 1);
+        const bool need_l = !halo_by_lanes && (tcol == 0), need_r = !halo_by_lanes && ((tcol == prm.TW - 1) || (tcol == LP - 1));
         const float lo = prm.relu ? 0.f : -__int_as_float(0x7f800000);
-        const int spu = 4 * nC16;                               // steps per unit
+        const int spu = 8 * nC32;                               // 16-channel steps per unit: 4 Winograd rows x 2 per slot
         const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total = my_units * spu;
-        // step n uses X buffer n % kFuXbufs (barrier xfull[n % (2*kFuXbufs)]) and A group n % kFuAGroups; this team
-        // takes n = team, team + 2, ...
-        static_assert(kFuXbufs >= 2 && kFuAGroups % 2 == 0, "each xfull barrier and each A group belongs to one team");
-        int xj = team, g = team % kFuAGroups, r = team;
-        uint32_t xph = 0, gph = 0;
+        // Step n = 16 input channels of one Winograd row; steps 2s and 2s+1 fill ring slot s, and slot s (A group
+        // s % 2 = the team's own) is taken by team s % 2: this team's k-th step is n = 4 * (k / 2) + 2 * team + k % 2.
+        // X buffer n % kFuXbufs, full-barrier n % kFuXfull.
+        static_assert(kFuAGroups == 2 && kFuXfull % 4 == 0, "each A group and each xfull barrier belongs to one team");
+        const int g = team;
         bool ok = true;
         int trt = 0; (void)trt;
-        for (int n = team; n < total; n += 2) {
-            const int i = r / nC16;
+        for (int k = 0;; ++k) {
+            const int n = 4 * (k >> 1) + 2 * team + (k & 1);
+            if (n >= total) break;
+            const int half = k & 1;                                // which 16 of the slot's 32 channels
+            const uint32_t gph = (uint32_t)(k >> 1) & 1u;          // the slot is this group's (k / 2)-th filling
+            const int r = n % spu, i = (r >> 1) / nC32;
+            const int xb = n % kFuXbufs, xj = n % kFuXfull;
+            const uint32_t xph = (uint32_t)(n / kFuXfull) & 1u;
             const bool strided = (i == 0 || i == 3);
             const int rows = strided ? prm.TH + 1 : 2 * prm.TH;
             const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
             const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
             const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
-            const int xb = xj < kFuXbufs ? xj : xj - kFuXbufs;
             if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            if (!mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
+            if (half == 0 && !mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
             const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
             tc_fence_after();
-            const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * 64);
+            const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * kFuGroupCols + half * 16);
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int c4 = 2 * hq + q;
                 float o[4][4];   // [j][channel within the quad]
 #pragma unroll
                 for (int cq = 0; cq < 4; ++cq) {
-                    // row i of B^T d at the tile's 4 pixels: the middle two from one 8-byte load per input row; the outer
-                    // two are the neighbouring tiles' middle values (warp shuffle), except at the ends of a tile row or of
-                    // the warp, where they are loaded
+                    // row i of B^T d at the tile's 4 pixels: the middle two from one 8-byte load per input row, the outer
+                    // two from the neighbouring lanes
                     const float *pa = xq + (c4 * 4 + cq) * chs;
                     const float *pb = pa + dab;
 #ifdef WG_TC_TRACE   // development build: bounds of the two 8-byte loads, recorded instead of faulting
@@ -368,8 +384,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
                     const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
                     float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
-                    if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
-                    if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
+                    if (!halo_by_lanes) {
+                        if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
+                        if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
+                    }
                     // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
                     o[0][cq] = fmaxf(r0 - r2, lo);
                     o[1][cq] = fmaxf(r1 + r2, lo);
@@ -377,7 +395,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     o[3][cq] = fmaxf(r1 - r3, lo);
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 16 + c4 * 4), o[j]);
+                for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
                 if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
             }
             // the tensor-memory writes have to be complete before the MMA issuer is told
@@ -391,9 +409,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 mbar_arrive(full_bar(g));
                 mbar_arrive(xempty_bar(xb));
             }
-            r += 2; if (r >= spu) r -= spu;
-            xj += 2; if (xj >= 2 * kFuXbufs) { xj -= 2 * kFuXbufs; xph ^= 1u; }
-            g += 2; if (g >= kFuAGroups) { g -= kFuAGroups; gph ^= 1u; }
         }
         (void)ok;
     } else {
@@ -538,7 +553,7 @@ static bool fused_geometry(FuParams &p)
     if (2 * (TH + 1) > 256) return false;    // TMA box extent
     p.nGroups = cdiv(p.B, p.NB);
     p.nKB = cdiv(p.K, kBlockN);
-    p.nC16 = p.C / 16;
+    p.nC32 = cdiv(p.C, 32);
     p.BWY = (2 * p.TW + 3) & ~3;
     p.xbytes1 = (uint32_t)((size_t)p.BW * 2 * TH * 16 * p.NB * 4);
     p.xbytes2 = (uint32_t)((size_t)p.BW * (TH + 1) * 16 * p.NB * 4);
@@ -583,10 +598,10 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     {
         cuuint64_t dims[3] = {(cuuint64_t)C, (cuuint64_t)K, 16};
         cuuint64_t strides[2] = {(cuuint64_t)C * 4, (cuuint64_t)K * C * 4};
-        cuuint32_t box[3] = {16, (cuuint32_t)kBlockN, 4};
+        cuuint32_t box[3] = {32, (cuuint32_t)kBlockN, 4};
         cuuint32_t estr[3] = {1, 1, 1};
         if (fn(&mapW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(prepared), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return WG2X2_ERR_LAUNCH;
     }
