@@ -38,7 +38,7 @@ constexpr int kFuWStages = kFuAGroups;            // a W stage travels with its 
 constexpr int kFuWTile = 64 * 128;                 // one [64 out-channels][32 channels] tile, rows of 128 bytes
 constexpr int kFuWBytes = 4 * kFuWTile;            // four of them, one per Winograd column j
 constexpr int kFuXbufs = 3;
-constexpr int kFuXfull = 4 * kFuXbufs;             // full-barriers of the X ring (see the kernel)
+constexpr int kFuXfull = 2 * kFuXbufs;             // full-barriers of the X ring (see the kernel)
 constexpr int kFuXbufBytes = 32768;
 constexpr int kFuTeamWarps = 8;                    // transform warps per team: one thread = one tile x 8 channels
 constexpr int kFuThreads = 256 + 256 + 2 * 32 * kFuTeamWarps;   // 2 control WGs, 2 epilogue WGs, 2 transform teams (2 WGs each)
@@ -49,7 +49,7 @@ static_assert(kFuSmemBytes <= 232448, "shared memory per CTA");
 // Register hand-over (setmaxnreg): the kernel starts with 64 registers per thread; the increase of the transform
 // warps can only be served from what the other warps of the same CTA have given back, and it blocks (for
 // ever) if that is not enough, so the three shares must fit into the launch allocation.
-constexpr int kFuRegsLaunch = 64, kFuRegsCtrl = 24, kFuRegsXf = 80, kFuRegsEpi = 64;
+constexpr int kFuRegsLaunch = 64, kFuRegsCtrl = 32, kFuRegsXf = 80, kFuRegsEpi = 64;
 static_assert(256 * kFuRegsCtrl + 256 * kFuRegsEpi + 2 * 32 * kFuTeamWarps * kFuRegsXf <= kFuRegsLaunch * kFuThreads,
               "setmaxnreg shares exceed the registers the CTA was launched with");
 
@@ -132,6 +132,14 @@ __device__ __forceinline__ void umma_tf32_ts_x2(uint32_t d_tmem, uint32_t a_tmem
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], [a1], b1, %4, q;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+// 8-byte shared-memory load from a 32-bit shared-space address.  Not volatile: the compiler may schedule it
+// freely among the arithmetic; it is kept after the barrier waits by the "memory" clobber of those.
+__device__ __forceinline__ float2 lds_f2(uint32_t addr)
+{
+    float2 v;
+    asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
 // 4 registers per thread -> this warp's 32 lanes x 4 consecutive 32-bit columns
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, const float *r)
 {
@@ -159,10 +167,10 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
     // barriers: full[G] (A group written by a team + its W tiles landed), free[G] (the four issuers' MMAs on the
     // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[2*XB], xempty[XB], ywritten[2], yfree[2].
-    // A step is 16 input channels; two consecutive steps (taken by the same team) fill one 32-channel slot.
-    // Step n fills X buffer n % XB but signals xfull[n % (4*XB)]: the two teams take turns on a buffer, and a
-    // parity wait can only tell a barrier's current phase from the one before it, so a waiter has to see every
-    // phase of the barrier it waits on; with teams changing every two steps xfull[j] is always the same team's.
+    // A step is 16 input channels; steps 2s and 2s+1 (one per team) fill the two halves of 32-channel slot s.
+    // Step n fills X buffer n % XB but signals xfull[n % (2*XB)]: with an odd XB the two teams take turns on a
+    // buffer, and a parity wait can only tell a barrier's current phase from the one before it, so a waiter has
+    // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
     constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
                   kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXfull, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
     static_assert((kB8 + 2) * 8 <= kCtrlBytes, "control block");
@@ -205,7 +213,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         g = u / prm.nRB;
     };
 
-    // registers: 1024 threads x 64 at launch; control warps keep 24, epilogue warps stay at 64, transform warps take 80
+    // registers: 1024 threads x 64 at launch; control warps keep 32, epilogue warps stay at 64, transform warps take 80
     if (warp < 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFuRegsCtrl));
         if (warp < 4 && lane == 0) {
@@ -331,21 +339,21 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int spu = 8 * nC32;                               // 16-channel steps per unit: 4 Winograd rows x 2 per slot
         const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total = my_units * spu;
-        // Step n = 16 input channels of one Winograd row; steps 2s and 2s+1 fill ring slot s, and slot s (A group
-        // s % 2 = the team's own) is taken by team s % 2: this team's k-th step is n = 4 * (k / 2) + 2 * team + k % 2.
+        // Step n = 16 input channels of one Winograd row; steps 2s and 2s+1 fill the two halves of ring slot s
+        // (A group s % 2).  This team takes the steps n = 2k + team, i.e. its own half of every slot, so the two
+        // teams work on a slot side by side and both see every phase of the slot's barriers.
         // X buffer n % kFuXbufs, full-barrier n % kFuXfull.
-        static_assert(kFuAGroups == 2 && kFuXfull % 4 == 0, "each A group and each xfull barrier belongs to one team");
-        const int g = team;
+        static_assert(kFuAGroups == 2 && kFuXfull % 2 == 0, "each xfull barrier belongs to one team");
+        const int half = team;                                 // which 16 of a slot's 32 channels
         bool ok = true;
         int trt = 0; (void)trt;
-        for (int k = 0;; ++k) {
-            const int n = 4 * (k >> 1) + 2 * team + (k & 1);
-            if (n >= total) break;
-            const int half = k & 1;                                // which 16 of the slot's 32 channels
-            const uint32_t gph = (uint32_t)(k >> 1) & 1u;          // the slot is this group's (k / 2)-th filling
-            const int r = n % spu, i = (r >> 1) / nC32;
-            const int xb = n % kFuXbufs, xj = n % kFuXfull;
-            const uint32_t xph = (uint32_t)(n / kFuXfull) & 1u;
+        // running values of n % kFuXfull (and its wrap parity), of the Winograd row and of the slot within the row
+        int xj = team, i = 0, c32 = 0;
+        uint32_t xph = 0;
+        for (int k = 0, n = team; n < total; ++k, n += 2) {
+            const int g = k & 1;
+            const uint32_t gph = (uint32_t)(k >> 1) & 1u;          // slot k is this group's (k / 2)-th filling
+            const int xb = xj < kFuXbufs ? xj : xj - kFuXbufs;
             const bool strided = (i == 0 || i == 3);
             const int rows = strided ? prm.TH + 1 : 2 * prm.TH;
             const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
@@ -354,10 +362,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            if (half == 0 && !mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
+            if (!mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
             const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
+            const uint32_t xq_s = xbase + (uint32_t)(xb * kFuXbufBytes + 4 * ((bi * 16 * rows + ra) * BW + 2 * twl + 4));   // the 8-byte loads, shared-space address
             tc_fence_after();
             const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * kFuGroupCols + half * 16);
 #pragma unroll
@@ -380,8 +389,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         }
                     }
 #endif
-                    const float2 am = *reinterpret_cast<const float2 *>(pa + 1);
-                    const float2 bm = *reinterpret_cast<const float2 *>(pb + 1);
+                    const float2 am = lds_f2(xq_s + (uint32_t)(4 * (c4 * 4 + cq) * chs));
+                    const float2 bm = lds_f2(xq_s + (uint32_t)(4 * ((c4 * 4 + cq) * chs + dab)));
                     const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
                     float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
                     if (!halo_by_lanes) {
@@ -409,6 +418,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 mbar_arrive(full_bar(g));
                 mbar_arrive(xempty_bar(xb));
             }
+            xj += 2; if (xj >= kFuXfull) { xj -= kFuXfull; xph ^= 1u; }
+            if (++c32 == nC32) { c32 = 0; i = (i + 1) & 3; }
         }
         (void)ok;
     } else {
