@@ -339,7 +339,8 @@ def main():
                     help="layer forward: the one-kernel path (X -> Y, V never stored), the two kernels, or (auto) whichever "
                          "wg2x2_layer_fwd_prepared picks for the shape")
     ap.add_argument("--fused", action="store_true", help="same as --path fused")
-    ap.add_argument("--net-layout", default="NHWC", choices=["NHWC", "NCHW"], help="cfg4: physical layout of the activations")
+    ap.add_argument("--net-layout", default="NCHW", choices=["NHWC", "NCHW"],
+                    help="cfg4: physical layout of the activations (NCHW: the 56x56 and 28x28 layers run as one kernel each)")
     ap.add_argument("--no-graph", action="store_true", help="cfg4: launch the network eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

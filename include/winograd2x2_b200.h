@@ -182,9 +182,20 @@ int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, flo
                              int C, int K, int layout, int relu, const float *out_scale, const float *out_shift,
                              const float *residual, void *stream);
 int wg2x2_layer_fwd_fused_supported(int B, int H, int W, int C, int K, int layout);
-/* The one-kernel layer forward on its own (NCHW in and out); WG2X2_ERR_UNSUPPORTED outside the shapes above. */
+/* The one-kernel layer forward on its own (NCHW in and out); WG2X2_ERR_UNSUPPORTED outside the shapes above.
+ * residual may be Y itself: the result is then added into Y in place (the TMA unit does the addition);
+ * otherwise residual is first copied to Y on the same stream and must not overlap it. */
 int wg2x2_layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
                           const float *out_scale, const float *out_shift, const float *residual, void *stream);
+/*
+ * The same with a per-input-channel affine map in front of the transform, x -> in_scale[c] * x + in_shift[c]
+ * inside the image (the padding stays zero): BatchNorm -> WinogradImTrans(relu) -> WinogradConv
+ * [-> BatchNorm + shortcut add] of ResNet-18-var/imagenet-resnet-transWino-prune.py:117-119 as one kernel.
+ * in_scale / in_shift: C floats each, both or neither NULL.
+ */
+int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K,
+                                 int relu, const float *in_scale, const float *in_shift, const float *out_scale,
+                                 const float *out_shift, const float *residual, void *stream);
 
 /*
  * Status word of the most recent kernel on this device that uses bounded waits

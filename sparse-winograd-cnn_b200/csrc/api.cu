@@ -32,7 +32,8 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
                      cudaStream_t st);
 bool fused_fwd_supported(int B, int H, int W, int C, int K, int layout);
 int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
-                    const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st);
+                    const float *in_scale, const float *in_shift, const float *out_scale, const float *out_shift,
+                    const float *residual, cudaStream_t st);
 size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW);
 int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *mask, float *dV, float *dW, int B, int H, int W,
                 int C, int K, int layout, int relu, void *ws, size_t ws_bytes, cudaStream_t st);
@@ -219,7 +220,7 @@ int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, flo
     const bool fused_pays = K <= 128 || (K <= 256 && C <= 64);
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) & 15u) == 0;   // TMA both ways
     if (fused_fwd_supported(B, H, W, C, K, layout) && aligned16 && (fused_pays || !V_scratch))
-        return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, out_scale, out_shift, residual, st);
+        return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, nullptr, nullptr, out_scale, out_shift, residual, st);
     if (!V_scratch) return WG2X2_ERR_WORKSPACE;
     const int nH = (H + 1) / 2, nW = (W + 1) / 2;
     const int s = imtrans_fwd(X, V_scratch, B, H, W, C, layout, relu, nullptr, nullptr, st);
@@ -231,7 +232,15 @@ int wg2x2_layer_fwd_fused(const float *X, const void *prepared, float *Y, int B,
                           const float *out_scale, const float *out_shift, const float *residual, void *stream)
 {
     if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
-    return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, out_scale, out_shift, residual, (cudaStream_t)stream);
+    return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, nullptr, nullptr, out_scale, out_shift, residual, (cudaStream_t)stream);
+}
+
+int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
+                                 const float *in_scale, const float *in_shift, const float *out_scale, const float *out_shift,
+                                 const float *residual, void *stream)
+{
+    if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    return layer_fwd_fused(X, prepared, Y, B, H, W, C, K, relu, in_scale, in_shift, out_scale, out_shift, residual, (cudaStream_t)stream);
 }
 
 int wg2x2_last_device_status(void *stream, unsigned int *where)

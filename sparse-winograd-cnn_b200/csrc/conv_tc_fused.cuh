@@ -55,7 +55,9 @@ static_assert(256 * kFuRegsCtrl + 256 * kFuRegsEpi + 2 * 32 * kFuTeamWarps * kFu
 
 struct FuParams {
     float *Y;
-    const float *out_scale, *out_shift, *residual;
+    const float *out_scale, *out_shift;
+    int accumulate;                        // Y already holds the shortcut: add to it (TMA reduce) instead of overwriting
+    const float *in_scale, *in_shift;      // per input channel, applied to the image before the transform (AFFINE)
     int B, H, W, C, K, nH, nW, outH, outW;
     int TH, TW, NB, BW, BWY;         // block of tiles; BW = width of the input box, BWY = of the output box
     int lp_log2;                     // a tile row takes 2^lp_log2 >= TW TMEM lanes
@@ -92,6 +94,14 @@ __device__ __forceinline__ void tma_store_4d(uint32_t src, const CUtensorMap *ma
 {
     asm volatile(
         "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%1, {%2, %3, %4, %5}], [%0];"
+        ::"r"(src), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+// the same box added to what global memory holds (element-wise fp32 add done by the TMA unit)
+__device__ __forceinline__ void tma_reduce_add_4d(uint32_t src, const CUtensorMap *map, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%1, {%2, %3, %4, %5}], [%0];"
         ::"r"(src), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
@@ -149,7 +159,7 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, const float *r)
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <bool EXTRAS>
+template <bool EXTRAS, bool AFFINE>
 __global__ void __launch_bounds__(kFuThreads, 1)
 layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
                        const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapY, const FuParams prm)
@@ -350,7 +360,25 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         // running values of n % kFuXfull (and its wrap parity), of the Winograd row and of the slot within the row
         int xj = team, i = 0, c32 = 0;
         uint32_t xph = 0;
+        // AFFINE: the image is s_c * x + t_c inside and 0 in the padding, so B^T d B = s_c * (B^T x B) + t_c * R_i * C_j
+        // with R = B^T rowmask, C = B^T colmask of the tile's 4 x 4 window (R = C = (0,2,0,0) away from the border)
+        int unit = blockIdx.x;
+        float Rm[4] = {0.f, 0.f, 0.f, 0.f}, Cm[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0, n = team; n < total; ++k, n += 2) {
+            if (AFFINE && i == 0 && c32 == 0) {
+                int gu, rbu, segu, kbu;
+                decode(unit, gu, rbu, segu, kbu);
+                unit += gridDim.x;
+                const int y0 = 2 * (rbu * prm.TH + thl) - 1, x0w = 2 * (segu * prm.TW + tcol) - 1;
+                float mr[4], mc[4];
+#pragma unroll
+                for (int d = 0; d < 4; ++d) {
+                    mr[d] = (y0 + d >= 0 && y0 + d < prm.H) ? 1.f : 0.f;
+                    mc[d] = (x0w + d >= 0 && x0w + d < prm.W) ? 1.f : 0.f;
+                }
+                Rm[0] = mr[0] - mr[2]; Rm[1] = mr[1] + mr[2]; Rm[2] = mr[2] - mr[1]; Rm[3] = mr[1] - mr[3];
+                Cm[0] = mc[0] - mc[2]; Cm[1] = mc[1] + mc[2]; Cm[2] = mc[2] - mc[1]; Cm[3] = mc[1] - mc[3];
+            }
             const int g = k & 1;
             const uint32_t gph = (uint32_t)(k >> 1) & 1u;          // slot k is this group's (k / 2)-th filling
             const int xb = xj < kFuXbufs ? xj : xj - kFuXbufs;
@@ -359,6 +387,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
             const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
             const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
+            const float Ri = AFFINE ? (i == 0 ? Rm[0] : i == 1 ? Rm[1] : i == 2 ? Rm[2] : Rm[3]) : 0.f;
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
@@ -398,10 +427,20 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
                     }
                     // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
-                    o[0][cq] = fmaxf(r0 - r2, lo);
-                    o[1][cq] = fmaxf(r1 + r2, lo);
-                    o[2][cq] = fmaxf(r2 - r1, lo);
-                    o[3][cq] = fmaxf(r1 - r3, lo);
+                    if (AFFINE) {
+                        const int chg = c32 * 32 + half * 16 + c4 * 4 + cq;
+                        const float sc = chg < prm.C ? __ldg(prm.in_scale + chg) : 0.f;
+                        const float tr = chg < prm.C ? __ldg(prm.in_shift + chg) * Ri : 0.f;
+                        o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tr * Cm[0]), lo);
+                        o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tr * Cm[1]), lo);
+                        o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tr * Cm[2]), lo);
+                        o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tr * Cm[3]), lo);
+                    } else {
+                        o[0][cq] = fmaxf(r0 - r2, lo);
+                        o[1][cq] = fmaxf(r1 + r2, lo);
+                        o[2][cq] = fmaxf(r2 - r1, lo);
+                        o[3][cq] = fmaxf(r1 - r3, lo);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
@@ -483,11 +522,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                                     const float s1 = __ldg(prm.out_scale + k), b1 = __ldg(prm.out_shift + k);
                                     y0 = fmaf(y0, s1, b1); y1 = fmaf(y1, s1, b1);
                                 }
-                                if (prm.residual && tile_ok && h < prm.outH) {
-                                    const float *rp = prm.residual + (((long long)b * prm.K + k) * prm.outH + h) * prm.outW + 2 * tw;
-                                    if ((prm.outW & 1) == 0) { const float2 r2 = __ldg(reinterpret_cast<const float2 *>(rp)); y0 += r2.x; y1 += r2.y; }
-                                    else { y0 += __ldg(rp); if (2 * tw + 1 < prm.outW) y1 += __ldg(rp + 1); }
-                                }
                             }
                             *reinterpret_cast<float2 *>(stage + my_off + c * TH * BWY) = make_float2(y0, y1);
                         }
@@ -499,7 +533,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     if (elected) {
                         stored = mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew);
                         if (stored && kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
-                            tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
+                            if (prm.accumulate) tma_reduce_add_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
+                            else tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
@@ -575,14 +610,23 @@ static bool fused_geometry(FuParams &p)
 }
 
 int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
-                    const float *out_scale, const float *out_shift, const float *residual, cudaStream_t st)
+                    const float *in_scale, const float *in_shift, const float *out_scale, const float *out_shift,
+                    const float *residual, cudaStream_t st)
 {
     if (!X || !prepared || !Y) return WG2X2_ERR_BAD_ARG;
+    if ((in_scale == nullptr) != (in_shift == nullptr)) return WG2X2_ERR_BAD_ARG;
     if (!fused_fwd_supported(B, H, W, C, K, WG2X2_NCHW)) return WG2X2_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) || (reinterpret_cast<uintptr_t>(Y) & 15u)) return WG2X2_ERR_BAD_ARG;
     if ((out_scale == nullptr) != (out_shift == nullptr)) return WG2X2_ERR_BAD_ARG;
     FuParams p;
-    p.Y = Y; p.out_scale = out_scale; p.out_shift = out_shift; p.residual = residual;
+    p.Y = Y; p.out_scale = out_scale; p.out_shift = out_shift;
+    // The shortcut is added by the TMA unit: Y receives it first (unless it is Y already), then every box is reduced
+    // into Y instead of stored.
+    p.accumulate = residual != nullptr;
+    if (residual && residual != Y &&
+        cudaMemcpyAsync(Y, residual, sizeof(float) * (size_t)B * K * H * W, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return WG2X2_ERR_LAUNCH;
+    p.in_scale = in_scale; p.in_shift = in_shift;
     p.B = B; p.H = H; p.W = W; p.C = C; p.K = K; p.outH = H; p.outW = W; p.relu = relu;
     if (!fused_geometry(p)) return WG2X2_ERR_UNSUPPORTED;
     EncodeTiledFn fn = encode_fn();
@@ -630,15 +674,14 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     // a grid that divides the units evenly: every CTA runs the same number of them
     const int rounds = cdiv(p.units, kNumSMs);
     const int grid = cdiv(p.units, rounds);
-    const bool extras = out_scale || residual;
-    if (extras) {
-        if (cudaFuncSetAttribute(layer_fwd_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess)
-            return WG2X2_ERR_LAUNCH;
-        layer_fwd_fused_kernel<true><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
-    } else {
-        if (cudaFuncSetAttribute(layer_fwd_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess)
-            return WG2X2_ERR_LAUNCH;
-        layer_fwd_fused_kernel<false><<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
-    }
+    const bool extras = out_scale != nullptr, affine = in_scale != nullptr;
+    auto launch = [&](auto kernel) -> bool {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess) return false;
+        kernel<<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
+        return true;
+    };
+    const bool launched = extras ? (affine ? launch(layer_fwd_fused_kernel<true, true>) : launch(layer_fwd_fused_kernel<true, false>))
+                                 : (affine ? launch(layer_fwd_fused_kernel<false, true>) : launch(layer_fwd_fused_kernel<false, false>));
+    if (!launched) return WG2X2_ERR_LAUNCH;
     return launch_status();
 }

@@ -7,8 +7,9 @@ the `a` blocks carry a 1x1 shortcut convolution + BatchNorm, the `b` blocks an i
 after a ReLU.  The reference has `pool4` commented out (:191), so its stage 5 runs at 14x14;
 `stage5_pool=True` restores the pool (7x7), which is the shape the benchmark configuration names.
 
-Only the Winograd layers run on this repository's kernels (NCHW); the stem, pools, 1x1 shortcuts,
-BatchNorm affine maps and the classifier are stock torch ops.  Weights are random (seeded): there is
+Only the Winograd layers run on this repository's kernels; the stem, pools, 1x1 shortcuts and the classifier
+are stock torch ops.  With layout="NCHW" the layers of the two high-resolution stages (56x56 and 28x28) run
+as one kernel each, BatchNorms and shortcut add included.  Weights are random (seeded): there is
 no checkpoint to load here.
 """
 import numpy as np
@@ -89,6 +90,21 @@ class _WinogradLayer(torch.nn.Module):
                                     residual=None if residual is None else self._to_kernel(residual, layout))
         return self._from_kernel(y, layout)
 
+    def onekernel_pays(self, x, layout):
+        """True where the whole layer (both BatchNorms, ReLU, products, shortcut add) runs as the one-kernel path."""
+        B, C, H, W = x.shape
+        return (layout == "NCHW" and (self.cout <= 128 or (self.cout <= 256 and C <= 64))
+                and wg2x2.fused_supported(B, H, W, C, self.cout, "NCHW"))
+
+    def forward_onekernel(self, x, bn_in, bn_out=None, residual=None):
+        """BatchNorm -> transform + ReLU -> product [-> BatchNorm + shortcut add] in one kernel (NCHW)."""
+        res = None if residual is None else residual.contiguous()
+        # the shortcut tensor is not used again: the kernel adds into it in place (no copy of it into a new output)
+        return wg2x2.layer_fwd_fused(x.contiguous(), self.prepared(), self.cout, relu=True, out=res,
+                                     in_scale=bn_in.scale, in_shift=bn_in.shift,
+                                     out_scale=None if bn_out is None else bn_out.scale,
+                                     out_shift=None if bn_out is None else bn_out.shift, residual=res)
+
     def forward_reference(self, x):
         """The same layer from the transform matrices with float64 einsums (for tests)."""
         BT = torch.tensor([[1, 0, -1, 0], [0, 1, 1, 0], [0, -1, 1, 0], [0, 1, 0, -1]], dtype=torch.float64, device=x.device)
@@ -104,12 +120,12 @@ class _WinogradLayer(torch.nn.Module):
 
 
 class ResNet18Var(torch.nn.Module):
-    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32", fused=True, layout="NHWC"):
+    def __init__(self, num_classes=1000, stage5_pool=True, seed=0, math="tf32", fused=True, layout="NCHW"):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
         self.math = math
-        # physical layout of the activations: "NHWC" keeps them channels-last (the reference's layout, and the one
-        # both cuDNN's and this library's kernels like best), "NCHW" keeps torch's default
+        # physical layout of the activations: "NCHW" (torch's default) lets the high-resolution layers run as one
+        # kernel each; "NHWC" keeps them channels-last (the reference's layout) on the two-kernel path
         self.layout = layout
         self.fused = fused      # fold BatchNorms and shortcut additions into the Winograd kernels (tensor-core path)
         self.stage5_pool = stage5_pool
@@ -132,8 +148,12 @@ class ResNet18Var(torch.nn.Module):
     def _block(self, blk, l, main, ref):
         """main + bn2c(conv(bn2b(conv(bn2a(l))))) with the Winograd layers as `ref` says."""
         if not ref and self.math == "tf32" and self.fused:
-            t = blk["w2a"].forward_fused(l, blk["bn2a"], layout=self.layout)
-            return blk["w2b"].forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main, layout=self.layout)
+            wa, wb = blk["w2a"], blk["w2b"]
+            t = (wa.forward_onekernel(l, blk["bn2a"]) if wa.onekernel_pays(l, self.layout)
+                 else wa.forward_fused(l, blk["bn2a"], layout=self.layout))
+            if wb.onekernel_pays(t, self.layout):
+                return wb.forward_onekernel(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main)
+            return wb.forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main, layout=self.layout)
         conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math, self.layout))
         t = conv(blk["w2a"], blk["bn2a"](l))
         t = conv(blk["w2b"], blk["bn2b"](t))

@@ -51,6 +51,7 @@ _SIGS = {
     "wg2x2_layer_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_layer_fwd_prepared": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
     "wg2x2_layer_fwd_fused": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "wg2x2_layer_fwd_fused_affine": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "wg2x2_layer_fwd_fused_supported": (_i, [_i, _i, _i, _i, _i, _i]),
     "wg2x2_last_device_status": (_i, [_p, ctypes.POINTER(ctypes.c_uint)]),
 }

@@ -197,14 +197,21 @@ def layer_fwd_prepared(x, prepared, K, relu=True, layout="NHWC", out=None, V_scr
     return Y
 
 
-def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shift=None, residual=None):
-    """The one-kernel layer forward (NCHW); raises Wg2x2Error(UNSUPPORTED) for other shapes."""
+def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shift=None, residual=None,
+                    in_scale=None, in_shift=None):
+    """The one-kernel layer forward (NCHW); raises Wg2x2Error(UNSUPPORTED) for other shapes.  in_scale/in_shift:
+    per-input-channel affine map applied to the image in front of the transform (the padding stays zero)."""
     _chk(x, "x")
     B, C, H, W = x.shape
     Y = out if out is not None else torch.empty((B, K, H, W), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(lib.wg2x2_layer_fwd_fused(_ptr(x), _ptr(prepared), _ptr(Y), B, H, W, C, K, int(bool(relu)), _ptr(out_scale),
-                                             _ptr(out_shift), _ptr(residual), _stream()), "wg2x2_layer_fwd_fused")
+        if in_scale is None and in_shift is None:
+            _lib.check(lib.wg2x2_layer_fwd_fused(_ptr(x), _ptr(prepared), _ptr(Y), B, H, W, C, K, int(bool(relu)), _ptr(out_scale),
+                                                 _ptr(out_shift), _ptr(residual), _stream()), "wg2x2_layer_fwd_fused")
+        else:
+            _lib.check(lib.wg2x2_layer_fwd_fused_affine(_ptr(x), _ptr(prepared), _ptr(Y), B, H, W, C, K, int(bool(relu)),
+                                                        _ptr(in_scale), _ptr(in_shift), _ptr(out_scale), _ptr(out_shift),
+                                                        _ptr(residual), _stream()), "wg2x2_layer_fwd_fused_affine")
     return Y
 
 

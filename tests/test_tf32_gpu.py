@@ -214,6 +214,30 @@ def test_fused_layer_forward(wg, oracle, shape):
     _status_ok(wg)
 
 
+@pytest.mark.parametrize("shape", FUSED_SHAPES + [(3, 9, 12, 32, 64), (2, 56, 56, 64, 128)])
+def test_fused_layer_forward_input_affine(wg, oracle, shape):
+    """BatchNorm-like map in front of the transform, inside the one kernel: the padding must stay zero, so the
+    oracle is fed s * x + t and pads that itself."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    rng = np.random.default_rng(5)
+    s_in, t_in = (1 + 0.3 * rng.standard_normal(C)).astype(np.float32), (0.5 * rng.standard_normal(C)).astype(np.float32)
+    s_out, b_out = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32), (0.3 * rng.standard_normal(K)).astype(np.float32)
+    R = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    xl = np.ascontiguousarray(np.transpose(X, (0, 3, 1, 2)))
+    prepared = wg.prepare_weights(_dev(Wt))
+    Xa = X.astype(np.float64) * s_in + t_in
+    for relu in (True, False):
+        want = oracle.conv_fwd(oracle.imtrans_fwd(Xa, relu=relu), Wt, H, W)
+        Y = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=relu, in_scale=_dev(s_in), in_shift=_dev(t_in))
+        assert oracle.max_rel(np.transpose(Y.cpu().numpy(), (0, 2, 3, 1)), want) <= TOL_TF32
+    Y2 = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=True, in_scale=_dev(s_in), in_shift=_dev(t_in), out_scale=_dev(s_out),
+                            out_shift=_dev(b_out), residual=_dev(np.ascontiguousarray(np.transpose(R, (0, 3, 1, 2)))))
+    want2 = oracle.conv_fwd(oracle.imtrans_fwd(Xa, relu=True), Wt, H, W) * s_out + b_out + R
+    assert oracle.max_rel(np.transpose(Y2.cpu().numpy(), (0, 2, 3, 1)), want2) <= TOL_TF32
+    _status_ok(wg)
+
+
 @pytest.mark.parametrize("shape,launches", [((256, 56, 56, 64, 64), 1500), ((40, 28, 28, 128, 128), 1500)])
 def test_fused_many_units_per_cta_repeated(wg, oracle, shape, launches):
     """Many units per CTA, many launches: every launch on the same input must give the same bits, the device
