@@ -67,10 +67,12 @@ class HostLayerPipeline:
                     self.s_run.wait_event(self.ev_out[i])     # the previous batch's yd[i] has been copied out
                 shape = self.vshape(hi - lo)
                 v = self.vflat[i % 2][:shape[0] * shape[1] * shape[2] * shape[3] * shape[4]].view(shape)
-                ops.imtrans_fwd(self.xd[i], relu=self.relu, layout=self.layout, out=v)
                 if prepared is not None:
-                    ops.conv_fwd_prepared(v, prepared, self.K, self.H, self.W, layout=self.layout, out=self.yd[i])
+                    # the library picks the one-kernel path where it pays (v is then unused), else the two kernels
+                    ops.layer_fwd_prepared(self.xd[i], prepared, self.K, relu=self.relu, layout=self.layout, out=self.yd[i],
+                                           V_scratch=v)
                 else:
+                    ops.imtrans_fwd(self.xd[i], relu=self.relu, layout=self.layout, out=v)
                     ops.conv_fwd(v, Wt, self.H, self.W, layout=self.layout, math=self.math, out=self.yd[i])
                 self.ev_run[i].record()
             with torch.cuda.stream(self.s_out):
