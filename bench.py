@@ -466,6 +466,23 @@ def main():
     if status != 0:
         raise RuntimeError("device status %d at %d" % (status, where))
 
+    # ---- for context next to the one-kernel line: the two-kernel path on the same inputs (short, outside the timed region)
+    two_kernel = None
+    if use_fused and rank == 0:
+        n2 = max(3, min(args.steps, 200))
+        e2 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        for i in range(3):
+            wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V); conv(i)
+        e2[0].record()
+        for i in range(n2):
+            wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
+        e2[1].record()
+        for i in range(n2):
+            conv(i)
+        e2[2].record()
+        torch.cuda.synchronize()
+        two_kernel = (e2[0].elapsed_time(e2[1]) / n2, e2[1].elapsed_time(e2[2]) / n2)
+
     # ---- end to end through the public call with host buffers ------------------------------
     Xpin = torch.from_numpy(Xh).pin_memory()
     Ypin = torch.empty(Y.shape, dtype=torch.float32).pin_memory()
@@ -538,6 +555,13 @@ def main():
     roof["traffic"] = measured_traffic.get((args.workload, B, args.layout, which))
     if use_fused:
         roof["kernels_ms"] = {"layer_fwd_fused": ms_k2}
+        if two_kernel is not None:
+            t1, t2 = two_kernel
+            roof["two_kernel_path"] = {
+                "note": "the same layer as input transform + product kernels with V through HBM (bench.py --path two-kernel), each "
+                        "launched back to back here; their own HBM roofline fractions",
+                "imtrans_fwd_ms": t1, "conv_fwd_ms": t2, "imtrans_fwd_frac": k1_bytes / (t1 * 1e-3) / 1e9 / pk["hbm_gbs"],
+                "conv_fwd_frac": k2_bytes / (t2 * 1e-3) / 1e9 / pk["hbm_gbs"], "layer_ms": t1 + t2}
     else:
         roof["kernels_ms"] = {"imtrans_fwd": ms_k1, "conv_fwd": ms_k2}
         roof["imtrans_fwd_gbs"] = k1_bytes / (ms_k1 * 1e-3) / 1e9
