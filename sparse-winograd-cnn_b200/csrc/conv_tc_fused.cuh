@@ -387,7 +387,9 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
             const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
             const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
+            // AFFINE: the shift term of this step is t_c * R_i * C_j
             const float Ri = AFFINE ? (i == 0 ? Rm[0] : i == 1 ? Rm[1] : i == 2 ? Rm[2] : Rm[3]) : 0.f;
+            const float RC0 = Ri * Cm[0], RC1 = Ri * Cm[1], RC2 = Ri * Cm[2], RC3 = Ri * Cm[3];
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
@@ -430,11 +432,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     if (AFFINE) {
                         const int chg = c32 * 32 + half * 16 + c4 * 4 + cq;
                         const float sc = chg < prm.C ? __ldg(prm.in_scale + chg) : 0.f;
-                        const float tr = chg < prm.C ? __ldg(prm.in_shift + chg) * Ri : 0.f;
-                        o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tr * Cm[0]), lo);
-                        o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tr * Cm[1]), lo);
-                        o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tr * Cm[2]), lo);
-                        o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tr * Cm[3]), lo);
+                        const float tc = chg < prm.C ? __ldg(prm.in_shift + chg) : 0.f;
+                        o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * RC0), lo);
+                        o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tc * RC1), lo);
+                        o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tc * RC2), lo);
+                        o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tc * RC3), lo);
                     } else {
                         o[0][cq] = fmaxf(r0 - r2, lo);
                         o[1][cq] = fmaxf(r1 + r2, lo);

@@ -182,7 +182,7 @@ def test_fused_affine_and_residual(wg, oracle, shape, layout):
 
 FUSED_SHAPES = [  # B, H, W, C, K  (NCHW, W % 4 == 0, C % 16 == 0)
     (2, 56, 56, 64, 64), (3, 28, 28, 128, 128), (5, 8, 8, 32, 64), (2, 12, 16, 16, 24), (9, 4, 4, 64, 96),
-    (1, 56, 72, 32, 32), (2, 7, 8, 48, 64),
+    (1, 56, 72, 32, 32), (2, 7, 8, 48, 64), (1, 6, 136, 16, 32), (2, 1, 4, 16, 16), (3, 2, 8, 32, 64), (1, 33, 60, 64, 72),
 ]
 
 
