@@ -390,6 +390,16 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             // AFFINE: the shift term of this step is t_c * R_i * C_j
             const float Ri = AFFINE ? (i == 0 ? Rm[0] : i == 1 ? Rm[1] : i == 2 ? Rm[2] : Rm[3]) : 0.f;
             const float RC0 = Ri * Cm[0], RC1 = Ri * Cm[1], RC2 = Ri * Cm[2], RC3 = Ri * Cm[3];
+            // AFFINE: this thread's 8 channels' scale and shift, fetched before the waits so that their latency hides there
+            float sc8[8], tc8[8];
+            if (AFFINE) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int chg = c32 * 32 + half * 16 + hq * 8 + c;
+                    sc8[c] = chg < prm.C ? __ldg(prm.in_scale + chg) : 0.f;
+                    tc8[c] = chg < prm.C ? __ldg(prm.in_shift + chg) : 0.f;
+                }
+            }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
@@ -430,9 +440,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     }
                     // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
                     if (AFFINE) {
-                        const int chg = c32 * 32 + half * 16 + c4 * 4 + cq;
-                        const float sc = chg < prm.C ? __ldg(prm.in_scale + chg) : 0.f;
-                        const float tc = chg < prm.C ? __ldg(prm.in_shift + chg) : 0.f;
+                        const float sc = sc8[q * 4 + cq], tc = tc8[q * 4 + cq];
                         o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * RC0), lo);
                         o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tc * RC1), lo);
                         o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tc * RC2), lo);
