@@ -30,6 +30,7 @@
 // tiles, one TMEM lane each) x 64 output channels.  Each input row is fetched once per Winograd row that uses
 // it (from L2 after the first time); HBM sees X once and Y once.
 #pragma once
+#include <type_traits>
 
 constexpr int kFuAGroups = 2;                      // ring of A groups in tensor memory; a group = four [128 x 32] tiles
 constexpr int kFuGroupCols = 4 * 32;               // tensor-memory columns of an A group
@@ -410,6 +411,9 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const uint32_t xq_s = xbase + (uint32_t)(xb * kFuXbufBytes + 4 * ((bi * 16 * rows + ra) * BW + 2 * twl + 4));   // the 8-byte loads, shared-space address
             tc_fence_after();
             const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * kFuGroupCols + half * 16);
+            // (two copies of the loop, so that the common case carries no test for the lanes at the ends of a tile row)
+            auto quads = [&](auto by_lanes_tag) {
+            constexpr bool kByLanes = decltype(by_lanes_tag)::value;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int c4 = 2 * hq + q;
@@ -434,7 +438,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     const float2 bm = lds_f2(xq_s + (uint32_t)(4 * ((c4 * 4 + cq) * chs + dab)));
                     const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
                     float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
-                    if (!halo_by_lanes) {
+                    if (!kByLanes) {
                         if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
                         if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
                     }
@@ -456,6 +460,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
                 if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
             }
+            };
+            if (halo_by_lanes) quads(std::true_type{}); else quads(std::false_type{});
             // the tensor-memory writes have to be complete before the MMA issuer is told
             tmem_st_wait();
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 6);
