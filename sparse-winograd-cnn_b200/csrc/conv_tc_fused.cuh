@@ -402,9 +402,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 }
             }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
-            if (!mbar_wait_warp(xfull_bar(xj), xph, abort_flag, 0xB00u | xj)) { ok = false; break; }
+            // both waits, then one vote (the warp converged and of one mind before the aligned instructions below)
+            const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj);
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            if (!mbar_wait_warp(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g)) { ok = false; break; }
+            const bool got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g);
+            if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
             const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
