@@ -499,8 +499,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
             int g, rb, seg, kb;
             decode(u, g, rb, seg, kb);
-            const int b = g * prm.NB + bi, th = rb * TH + thl, tw = seg * prm.TW + twl;
-            const bool tile_ok = live && b < prm.B && th < prm.nH && tw < prm.nW;
             const int kbase = kb * kBlockN + half * 32;
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
@@ -530,7 +528,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
                     float *stage = stage0 + (st_use & 1u) * box_floats;
                     if (live) {
-                        const int h = 2 * th + a;
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int k = kbase + rd * 16 + c;
