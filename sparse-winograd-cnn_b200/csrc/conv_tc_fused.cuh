@@ -2,7 +2,7 @@
 // nor the 16 Winograd-domain products ever exist outside the SM.  Included by conv_tc.cu.
 //
 // Both transforms ride on the tensor core's operands:
-//   * input side: the A operand of every MMA (row i, column j of B^T d B for 128 tiles x 16 channels, after
+//   * input side: the A operand of every MMA (row i, column j of B^T d B for 128 tiles x 8 channels, after
 //     the ReLU) is computed by the transform warps and written with tcgen05.st into tensor memory
 //     (lane = tile, column = channel); tcgen05.mma reads it from there;
 //   * output side: y[a][e] = sum_ij At[a][i] At[e][j] (V_ij . W_ij) is linear in the products and the
@@ -10,25 +10,31 @@
 //     accumulators (a, e) it contributes to, with the instruction descriptor's negate bit for the minus
 //     signs.  That costs 36 instead of 16 MMAs per 8 channels (the tensor core has the room) and leaves four
 //     128x64 accumulators per unit instead of sixteen products: the epilogue only copies.
-// One step = one Winograd row i of one block of tiles for 16 input channels:
-//   * the X producer (warp 0) brings, by TMA, the input rows that step needs into a ring of shared-memory
+// A ring slot = one Winograd row i of one block of tiles for 32 input channels (four [128 x 32] A tiles in
+// tensor memory + four [64 x 32] weight tiles in shared memory); a step = one 16-channel half of a slot:
+//   * the X producer (warp 4) brings, by TMA, the input rows a step needs into a ring of shared-memory
 //     buffers: rows d1,d2 of every tile for i = 1, 2 (a dense box), rows d0,d2 (i = 0) or d1,d3 (i = 3) through
 //     a tensor map that walks the image with a row stride of 2, so only the rows that are used travel;
-//     out-of-image rows and columns arrive as zeros, which is the layer's padding;
-//   * two teams of eight transform warps take alternate steps (while one team waits for loads or for the
-//     tensor core, the other issues); a thread owns one tile x 8 channels;
-//   * the W producer (warp 2) streams the step's four [64 x 16] weight tiles (B operands) into the same ring
-//     slot the A group belongs to;
-//   * two MMA issuers (warps 1 and 3), one per output column e: a single issuing thread gets too few issue
-//     slots next to the transform warps to keep the tensor core fed, and each accumulator has one owner.
-//     (Roles must not share a warp: a lane that waits on an mbarrier stalls the other lanes of its warp too.)
+//     out-of-image rows, columns and channels arrive as zeros, which is the layer's padding;
+//   * two teams of eight transform warps fill the two halves of every slot side by side; a thread owns one
+//     tile x 8 channels: two 8-byte loads per channel give the middle pixels of its window, the outer two come
+//     from the neighbouring lanes by shuffle; an optional per-channel affine map (a BatchNorm in front of the
+//     layer) is applied on the fly without touching the zero padding;
+//   * the W producer (warp 6) streams the slot's four weight tiles (B operands);
+//   * four MMA issuers (warps 0..3, one thread each), one per output accumulator (a, e): a single issuing
+//     thread gets too few issue slots next to the transform warps to keep the tensor core fed, and each
+//     accumulator has one owner.  (Roles must not share a warp: a lane that waits on an mbarrier stalls the
+//     other lanes of its warp too.)
 //   * the eight epilogue warps read output row a = 0 as soon as Winograd row 2 is done (row 3 does not touch
-//     it) and row a = 1 after row 3, stage 16 channels at a time in shared memory and hand the box to a TMA
-//     store (row stride 2 in Y), which also clips odd sizes and partial blocks.
-// Tensor memory: columns 0..255 = the accumulators (a, e) at (2a + e) * 64, 256..511 = a ring of four A
-// groups (4 tiles x 16 columns each).  A unit is NB images x TH tile rows x TW tile columns (at most 128
-// tiles, one TMEM lane each) x 64 output channels.  Each input row is fetched once per Winograd row that uses
-// it (from L2 after the first time); HBM sees X once and Y once.
+//     it) and row a = 1 after row 3, stage 16 channels at a time in shared memory (optional per-channel
+//     affine) and hand the box to a TMA store (row stride 2 in Y), which also clips odd sizes and partial
+//     blocks -- or to a TMA reduce-add when Y already holds a shortcut to add to.
+// Tensor memory: columns 0..255 = the accumulators (a, e) at (2a + e) * 64, 256..511 = a ring of two A groups
+// (4 tiles x 32 columns each).  A unit is NB images x TH tile rows x TW tile columns (at most 128 tiles, one
+// TMEM lane each; a tile row takes a power-of-two number of lanes) x 64 output channels.  Each input row is
+// fetched once per Winograd row that uses it (from L2 after the first time); HBM sees X once and Y once.
+// Every waiter sees every phase of a barrier it waits on (a parity wait cannot tell a phase from the one two
+// before it); all waits are bounded and end in a status word instead of a hang.
 #pragma once
 #include <type_traits>
 
