@@ -182,7 +182,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     const uint32_t wbase = base + kWOff, xbase = base + kXOff, bars = base + kBarOff;
     const float *xgen = reinterpret_cast<const float *>(gen_base + kXOff);
     uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
-    // barriers: full[G] (A group written by a team + its W tiles landed), free[G] (the four issuers' MMAs on the
+    // barriers: full[G] (both halves of the A group written, one by each team, and the W tiles landed), free[G] (the four issuers' MMAs on the
     // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[2*XB], xempty[XB], ywritten[2], yfree[2].
     // A step is 16 input channels; steps 2s and 2s+1 (one per team) fill the two halves of 32-channel slot s.
     // Step n fills X buffer n % XB but signals xfull[n % (2*XB)]: with an odd XB the two teams take turns on a
@@ -470,7 +470,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             }
             };
             if (halo_by_lanes) quads(std::true_type{}); else quads(std::false_type{});
-            // the tensor-memory writes have to be complete before the MMA issuer is told
+            // the tensor-memory writes have to be complete before the MMA issuers are told
             tmem_st_wait();
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 6);
             tc_fence_before();
