@@ -238,6 +238,35 @@ def test_fused_layer_forward_input_affine(wg, oracle, shape):
     _status_ok(wg)
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_fused_random_shapes(wg, oracle, seed):
+    """Random geometry (segments, row blocks, images per unit, ragged ends, channel counts) against the oracle,
+    plain and with every optional map at once."""
+    rng = np.random.default_rng(1000 + seed)
+    B, H = int(rng.integers(1, 7)), int(rng.integers(1, 40))
+    W = 4 * int(rng.integers(1, 40))
+    C, K = 16 * int(rng.integers(1, 7)), int(rng.integers(1, 150))
+    shape = (B, H, W, C, K)
+    assert wg.fused_supported(B, H, W, C, K, "NCHW"), shape
+    X, Wt = _inputs(shape)
+    xl = np.ascontiguousarray(np.transpose(X, (0, 3, 1, 2)))
+    prepared = wg.prepare_weights(_dev(Wt))
+    Y = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=True)
+    want = oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)
+    err = oracle.max_rel(np.transpose(Y.cpu().numpy(), (0, 2, 3, 1)), want)
+    assert err <= TOL_TF32, (shape, err)
+    s_in, t_in = (1 + 0.3 * rng.standard_normal(C)).astype(np.float32), (0.5 * rng.standard_normal(C)).astype(np.float32)
+    s_out, b_out = (1 + 0.2 * rng.standard_normal(K)).astype(np.float32), (0.3 * rng.standard_normal(K)).astype(np.float32)
+    R = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    y = _dev(np.ascontiguousarray(np.transpose(R, (0, 3, 1, 2))))          # the shortcut, added to in place
+    Y2 = wg.layer_fwd_fused(_dev(xl), prepared, K, relu=True, out=y, in_scale=_dev(s_in), in_shift=_dev(t_in),
+                            out_scale=_dev(s_out), out_shift=_dev(b_out), residual=y)
+    want2 = oracle.conv_fwd(oracle.imtrans_fwd(X.astype(np.float64) * s_in + t_in, relu=True), Wt, H, W) * s_out + b_out + R
+    err2 = oracle.max_rel(np.transpose(Y2.cpu().numpy(), (0, 2, 3, 1)), want2)
+    assert err2 <= TOL_TF32, (shape, err2)
+    _status_ok(wg)
+
+
 @pytest.mark.parametrize("shape,launches", [((256, 56, 56, 64, 64), 1500), ((40, 28, 28, 128, 128), 1500)])
 def test_fused_many_units_per_cta_repeated(wg, oracle, shape, launches):
     """Many units per CTA, many launches: every launch on the same input must give the same bits, the device
