@@ -44,12 +44,13 @@ constexpr int kFuACol0 = 4 * kBlockN;              // first tensor-memory column
 constexpr int kFuWStages = kFuAGroups;            // a W stage travels with its A group: one "slot" of the ring
 constexpr int kFuWTile = 64 * 128;                 // one [64 out-channels][32 channels] tile, rows of 128 bytes
 constexpr int kFuWBytes = 4 * kFuWTile;            // four of them, one per Winograd column j
-constexpr int kFuXbufs = 3;
+constexpr int kFuXbufs = 4;
 constexpr int kFuXfull = 2 * kFuXbufs;             // full-barriers of the X ring (see the kernel)
 constexpr int kFuXbufBytes = 32768;
 constexpr int kFuTeamWarps = 8;                    // transform warps per team: one thread = one tile x 8 channels
 constexpr int kFuThreads = 256 + 256 + 2 * 32 * kFuTeamWarps;   // 2 control WGs, 2 epilogue WGs, 2 transform teams (2 WGs each)
-constexpr int kFuYStageBytes = kFuXbufBytes;      // per epilogue warpgroup: two [NB][16 channels][TH rows][2*TW pixels] boxes of Y
+constexpr int kFuYStageBytes = kFuXbufBytes / 2;  // per epilogue warpgroup: one [NB][16 channels][TH rows][2*TW pixels] box of Y
+                                                   // (a fourth X buffer is worth more than a second box: 50.9 vs 53.8 us)
 constexpr int kFuSmemBytes = kFuWStages * kFuWBytes + kFuXbufs * kFuXbufBytes + 2 * kFuYStageBytes + kCtrlBytes + 1024;
 static_assert(kFuACol0 + kFuAGroups * kFuGroupCols <= (int)kTmemCols, "tensor memory columns");
 static_assert(kFuSmemBytes <= 232448, "shared memory per CTA");
@@ -496,7 +497,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int row_e = live ? trow : 0, twl = live ? tcol : 0;
         const int bi = row_e / prm.TH, thl = row_e - bi * prm.TH;
         const int BWY = prm.BWY, TH = prm.TH;
-        const int box_floats = prm.NB * 16 * TH * BWY;           // one staged box
         float *stage0 = reinterpret_cast<float *>(gen_base + kYOff + half * kFuYStageBytes);
         const int my_off = (bi * 16 * TH + thl) * BWY + 2 * twl; // this thread's tile in channel 0 of a box
         const bool elected = ((ew & 3) == 0) && lane == 0;
@@ -526,13 +526,13 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acce_bar(a));
                     }
-                    // the store before last of this warpgroup has left its half of the staging area
+                    // the previous store of this warpgroup has left the staging area
                     if (elected) {
-                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                         mbar_arrive(yfree_bar(half));
                     }
                     if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
-                    float *stage = stage0 + (st_use & 1u) * box_floats;
+                    float *stage = stage0;
                     if (live) {
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
