@@ -548,9 +548,9 @@ def main():
     roof["frac"] = roof["achieved"] / roof["peak"]
     # dram__bytes_read.sum + dram__bytes_write.sum per launch from the one-pass ncu captures summarised
     # under profiles/ (taken at this workload's full size); None for shapes that were not captured
-    # (the fused kernel's 61.2 MB = 51.8 MB read + 9.4 MB written inside the launch: most of Y is still dirty in L2 when
+    # (the fused kernel's 60.0 MB = 51.7 MB read + 8.3 MB written inside the launch: most of Y is still dirty in L2 when
     # the kernel ends and reaches DRAM later; algorithmic X + W + Y = 103 MB)
-    measured_traffic = {("cfg2", 64, "NCHW", "imtrans"): 197.8e6, ("cfg2", 64, "NCHW", "conv"): 224.7e6, ("cfg2", 64, "NCHW", "fused"): 61.2e6}
+    measured_traffic = {("cfg2", 64, "NCHW", "imtrans"): 197.8e6, ("cfg2", 64, "NCHW", "conv"): 224.7e6, ("cfg2", 64, "NCHW", "fused"): 60.0e6}
     which = "fused" if use_fused else ("conv" if roof["kernel"].startswith("conv") else "imtrans")
     roof["traffic"] = measured_traffic.get((args.workload, B, args.layout, which))
     if use_fused:
