@@ -61,6 +61,12 @@ constexpr int kFuRegsLaunch = 64, kFuRegsCtrl = 32, kFuRegsXf = 80, kFuRegsEpi =
 static_assert(256 * kFuRegsCtrl + 256 * kFuRegsEpi + 2 * 32 * kFuTeamWarps * kFuRegsXf <= kFuRegsLaunch * kFuThreads,
               "setmaxnreg shares exceed the registers the CTA was launched with");
 
+#ifdef WG_TC_TRACE   // development aid: wall-clock stamps (ns) of every CTA at entry, after set-up and at its end
+#define FU_CTA_STAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 200) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_tc_trace[3200 + 4 * blockIdx.x + (k)] = (long long)t_; } } while (0)
+#else
+#define FU_CTA_STAMP(k) do { } while (0)
+#endif
+
 struct FuParams {
     float *Y;
     const float *out_scale, *out_shift;
@@ -204,6 +210,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + kB8 + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    FU_CTA_STAMP(0);
 
     if (threadIdx.x == 0) {
         for (int g = 0; g < kFuAGroups; ++g) { mbar_init(full_bar(g), 2 * kFuTeamWarps + 1); mbar_init(free_bar(g), 4); }
@@ -222,6 +229,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
+    FU_CTA_STAMP(1);
 
     const int nC32 = prm.nC32;
     auto decode = [&](int u, int &g, int &rb, int &seg, int &kb) {
@@ -252,11 +260,9 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             int i = 0, cc = 0;
             uint32_t units_done = 0;
             int trm = 0; (void)trm;
-            // the slot's barrier is probed one step ahead, so that the probe's latency hides behind the MMAs
-            bool ready = total > 0 && mbar_try_wait(full_bar(0), 0);
             for (int n = 0; n < total; ++n) {
                 if (warp == 0) TC_TRACE(1024 + 5 * trm);
-                if (!ready && !mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g)) break;
+                if (!mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g)) break;
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 1);
                 // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
                 if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a)) break;
@@ -264,7 +270,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 tc_fence_after();
                 int g2 = g + 1; uint32_t gph2 = gph;
                 if (g2 == kFuAGroups) { g2 = 0; gph2 ^= 1u; }
-                ready = (n + 1 < total) && mbar_try_wait(full_bar(g2), gph2);
                 if (i >= a && i <= a + 2) {
                     const bool neg_a = (a == 1 && i >= 2);
                     const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
@@ -433,7 +438,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     // two from the neighbouring lanes
                     const float *pa = xq + (c4 * 4 + cq) * chs;
                     const float *pb = pa + dab;
-#ifdef WG_TC_TRACE   // development build: bounds of the two 8-byte loads, recorded instead of faulting
+#ifdef WG_TC_BOUNDS   // development build: bounds of the two 8-byte loads, recorded instead of faulting
                     {
                         const long long oa = (pa + 1) - xgen, ob = (pb + 1) - xgen;
                         if (oa < 0 || ob < 0 || oa + 1 >= kFuXbufs * (kFuXbufBytes / 4) || ob + 1 >= kFuXbufs * (kFuXbufBytes / 4) || (oa & 1) || (ob & 1)) {
@@ -574,6 +579,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     __syncwarp();                        // the lanes of a warp took different roles: together again before the aligned instructions
     tc_fence_before();
     __syncthreads();
+    FU_CTA_STAMP(2);
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
