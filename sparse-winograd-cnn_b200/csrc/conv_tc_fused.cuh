@@ -230,6 +230,12 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_ptr_slot;
     FU_CTA_STAMP(1);
+    // Launched with programmatic stream serialisation, this grid may have been scheduled while the kernel before it in
+    // the stream was still running (on SMs that one left free, or as its CTAs ended): everything up to here touched
+    // no global memory.  Let the next launch do the same, then wait for the previous grid to have completed and its
+    // writes to be visible.  (Both instructions do nothing in a launch without the attribute.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int nC32 = prm.nC32;
     auto decode = [&](int u, int &g, int &rb, int &seg, int &kb) {
@@ -702,10 +708,23 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     const int rounds = cdiv(p.units, kNumSMs);
     const int grid = cdiv(p.units, rounds);
     const bool extras = out_scale != nullptr, affine = in_scale != nullptr;
+    // Back-to-back layers: the next launch's scheduling and set-up overlap this kernel's tail (programmatic dependent
+    // launch; the kernel waits for its predecessor before its first global access).  Not while a graph is being
+    // captured, and WG2X2_PDL=0 in the environment turns it off.
+    static const bool pdl_env = [] { const char *e = getenv("WG2X2_PDL"); return !(e && e[0] == '0'); }();
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    const bool pdl = pdl_env && capturing == cudaStreamCaptureStatusNone;
     auto launch = [&](auto kernel) -> bool {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFuSmemBytes) != cudaSuccess) return false;
-        kernel<<<grid, kFuThreads, kFuSmemBytes, st>>>(mapX1, mapX2, mapW, mapY, p);
-        return true;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((unsigned)kFuThreads);
+        cfg.dynamicSmemBytes = kFuSmemBytes; cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+        return cudaLaunchKernelEx(&cfg, kernel, mapX1, mapX2, mapW, mapY, p) == cudaSuccess;
     };
     const bool launched = extras ? (affine ? launch(layer_fwd_fused_kernel<true, true>) : launch(layer_fwd_fused_kernel<true, false>))
                                  : (affine ? launch(layer_fwd_fused_kernel<false, true>) : launch(layer_fwd_fused_kernel<false, false>));
