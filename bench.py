@@ -533,7 +533,9 @@ def main():
                     achieved=fb / (ms_k2 * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"],
                     note="only X, W and Y cross HBM (%.1f MB); the kernel is paced by the SM, not by HBM: per 128 tiles x 64 channels x "
                          "64 output channels it issues 288 tcgen05.mma (N=64, K=8; the output transform is folded into 36 signed MMAs per 8 "
-                         "channels instead of 16) and its transform warps compute 16 x 128 x 64 values" % (fb / 1e6),
+                         "channels instead of 16) and its transform warps compute 16 x 128 x 64 values.  achieved = bytes / the duration of a "
+                         "launch bracketed by events on its own (kernels_ms); back to back the launches overlap their neighbours' tails "
+                         "(programmatic dependent launch), which is why ms_per_step can be below it" % (fb / 1e6),
                     tensor_tflops_algorithmic=flops / (ms_k2 * 1e-3) / 1e12, tensor_tflops_issued=2.25 * flops / (ms_k2 * 1e-3) / 1e12)
     elif ms_k2 >= ms_k1:
         if args.math == "tf32" and k2_t_tensor > k2_t_hbm:
