@@ -92,6 +92,69 @@ __global__ void __launch_bounds__(256) conv_dm_nchw_kernel(const float *__restri
     }
 }
 
+// The same with four channels per lane: 16-byte plane stores, 512 bytes per warp and store with LC = 32 lanes along
+// the channels (128 per CTA), 256 bytes with LC = 16 (64 per CTA, the two halves of a warp on two tiles at once).
+// Where the band is the whole image, the CTA's channels are one contiguous run of dY and are staged as such.
+template <int LC>
+__global__ void __launch_bounds__(256, 3) conv_dm_nchw_vec_kernel(const float *__restrict__ dY, float *__restrict__ dM, long long P, int nH,
+                                                                    int nW, int H, int W, int K, int R, int nbands, int pitch)
+{
+    constexpr int CB = 4 * LC, QW = 32 / LC;
+    extern __shared__ float S[];
+    const int band = blockIdx.x % nbands;
+    const int b = blockIdx.x / nbands;
+    const int k0 = blockIdx.y * CB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lc = lane % LC, lq = lane / LC;
+    const int th0 = band * R;
+    const int rows_tile = min(R, nH - th0);
+    const int lo = 2 * th0, hi = min(2 * th0 + 2 * rows_tile, H);
+    const int nfill = (hi - lo) * W;
+    const int nch = min(CB, K - k0);
+    if (nfill == H * W) {
+        const float *src = dY + ((long long)b * K + k0) * nfill;
+        for (int k = threadIdx.x; k < nch * nfill; k += 256) {
+            const int kk = k / nfill;
+            S[kk * pitch + (k - kk * nfill)] = __ldg(src + k);
+        }
+    } else {
+        for (int kk = warp; kk < nch; kk += 8) {
+            const float *src = dY + (((long long)b * K + k0 + kk) * H + lo) * W;
+            float *dst = S + kk * pitch;
+            for (int i = lane; i < nfill; i += 32) dst[i] = __ldg(src + i);
+        }
+    }
+    __syncthreads();
+    if (k0 + 4 * lc >= K) return;
+    const float *Sk = S + 4 * lc * pitch;
+#pragma unroll 1
+    for (int q = warp * QW + lq; q < rows_tile * nW; q += 8 * QW) {
+        const int tr = q / nW, tw = q - tr * nW;
+        float g[4][2][2];
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int h = lo + 2 * tr + a, w = 2 * tw + e;
+                    g[v][a][e] = (h < H && w < W) ? Sk[v * pitch + (2 * tr + a) * W + w] : 0.f;
+                }
+        float m0[4][4], m1[4][4], m2[4][4], m3[4][4];
+        a_g_at(g[0][0][0], g[0][0][1], g[0][1][0], g[0][1][1], m0);
+        a_g_at(g[1][0][0], g[1][0][1], g[1][1][0], g[1][1][1], m1);
+        a_g_at(g[2][0][0], g[2][0][1], g[2][1][0], g[2][1][1], m2);
+        a_g_at(g[3][0][0], g[3][0][1], g[3][1][0], g[3][1][1], m3);
+        const long long p = ((long long)b * nH + th0 + tr) * nW + tw;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<float4 *>(dM + ((long long)(4 * i + j) * P + p) * K + k0 + 4 * lc) =
+                    make_float4(round_tf32(m0[i][j]), round_tf32(m1[i][j]), round_tf32(m2[i][j]), round_tf32(m3[i][j]));
+    }
+}
+
 __global__ void __launch_bounds__(256) round_tf32_kernel(const float *__restrict__ src, float *__restrict__ dst, long long n)
 {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -104,6 +167,27 @@ static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int
     const long long P = (long long)B * nH * nW;
     if (layout == WG2X2_NHWC) {
         conv_dm_nhwc_kernel<<<(unsigned)cdivll(P * (K / 4), 256), 256, 0, st>>>(dY, dM, P, nH, nW, H, W, K);
+    } else if (K % 4 == 0 && K >= 64 && 2 * W <= 192 && (reinterpret_cast<uintptr_t>(dM) & 15u) == 0) {
+        // four channels per lane; 128 channels per CTA where a band of them stays below 50 KB, else 64
+        const bool wide = K >= 128 && 2 * W <= 96;
+        const int cb = wide ? 128 : 64;
+        int R = (wide ? 96 : 192) / (2 * W);
+        if (R > nH) R = nH;
+        const int nbands = cdiv(nH, R);
+        R = cdiv(nH, nbands);
+        const int pitch = (2 * R * W) | 1;
+        const int smem = cb * pitch * (int)sizeof(float);
+        if ((long long)B * nbands > 0x7fffffffLL || cdiv(K, cb) > 65535) return WG2X2_ERR_UNSUPPORTED;
+        const dim3 grid((unsigned)(B * nbands), cdiv(K, cb));
+        if (wide) {
+            if (cudaFuncSetAttribute(conv_dm_nchw_vec_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return WG2X2_ERR_LAUNCH;
+            conv_dm_nchw_vec_kernel<32><<<grid, 256, smem, st>>>(dY, dM, P, nH, nW, H, W, K, R, nbands, pitch);
+        } else {
+            if (cudaFuncSetAttribute(conv_dm_nchw_vec_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                return WG2X2_ERR_LAUNCH;
+            conv_dm_nchw_vec_kernel<16><<<grid, 256, smem, st>>>(dY, dM, P, nH, nW, H, W, K, R, nbands, pitch);
+        }
     } else {
         int R = 384 / (2 * W);
         if (R < 1) R = 1;

@@ -19,6 +19,9 @@ __device__ __forceinline__ float4 fma_of(float4 a, float4 s, float4 b) { return 
 __device__ __forceinline__ float fma_of(float a, float s, float b) { return fmaf(a, s, b); }
 __device__ __forceinline__ float4 relu_of(float4 a) { return make_float4(fmaxf(a.x, 0.f), fmaxf(a.y, 0.f), fmaxf(a.z, 0.f), fmaxf(a.w, 0.f)); }
 __device__ __forceinline__ float relu_of(float a) { return fmaxf(a, 0.f); }
+// the components of a value to p[0], p[pitch], ... (by name: indexing through a pointer would put the value on the stack)
+__device__ __forceinline__ void put_lanes(float *p, int pitch, float4 v) { p[0] = v.x; p[pitch] = v.y; p[2 * pitch] = v.z; p[3 * pitch] = v.w; }
+__device__ __forceinline__ void put_lanes(float *p, int, float v) { p[0] = v; }
 __device__ __forceinline__ float4 keep_where_pos(float4 g, float4 m) { return make_float4(m.x > 0.f ? g.x : 0.f, m.y > 0.f ? g.y : 0.f, m.z > 0.f ? g.z : 0.f, m.w > 0.f ? g.w : 0.f); }
 __device__ __forceinline__ float keep_where_pos(float g, float m) { return m > 0.f ? g : 0.f; }
 
@@ -323,41 +326,80 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_kernel(const float *__re
     }
 }
 
-// NCHW, image rows up to 192 pixels: the same gather with lane = channel over a band of R tile rows;
-// the 2R x W output pixels of each channel collect in shared memory (odd pitch between channels) and
-// leave as one contiguous run per channel.
-template <bool MASK>
-__global__ void __launch_bounds__(256) imtrans_bwd_nchw_band_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
-                                                                      float *__restrict__ dX, int B, int H, int W, int C, int nH,
-                                                                      int nW, int R, int nbands, int pitch)
+// NCHW, image rows up to 192 pixels: the same gather with lane = VEC consecutive channels over a band of R tile
+// rows; the 2R x W output pixels of each channel collect in shared memory (odd pitch between channels) and
+// leave as one contiguous run per channel -- or, where the band is the whole image, as one contiguous run for
+// all the block's channels.  VEC = 4 reads dV (and the ReLU mask) with 16-byte loads: LC = 32 lanes along the
+// channels (128 per block, 512 bytes per request) where such a band fits four blocks per SM, else LC = 16 (64
+// channels per block, the two halves of a warp on two tiles at once).
+template <int VEC, int LC, bool MASK>
+__global__ void __launch_bounds__(256, 4) imtrans_bwd_nchw_band_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                         float *__restrict__ dX, int B, int H, int W, int C, int nH,
+                                                                         int nW, int R, int nbands, int pitch)
 {
-    extern __shared__ float O[];   // [32 channels][pitch]
-    const int band = blockIdx.x % nbands;
-    const int b = blockIdx.x / nbands;
-    const int c0 = blockIdx.y * 32;
+    using T = typename Vec<VEC>::type;
+    constexpr int CB = LC * VEC;             // channels per block
+    constexpr int QW = 32 / LC;              // tiles a warp works on at once
+    extern __shared__ float O[];             // [CB channels][pitch]
+    // Block order.  One input stream: a one-dimensional grid with the channel blocks fastest, so that neighbouring
+    // blocks read neighbouring segments of every dV row.  With the mask (32 streams of rows open at once) that
+    // order measured slower than images fastest, which is the two-dimensional grid (66 vs 78 us on
+    // 256 x 512 x 7 x 7; without the mask 50 vs 58 us the other way).
+    int c0, bb;
+    if (MASK) {
+        c0 = blockIdx.y * CB;
+        bb = blockIdx.x;
+    } else {
+        const int ncb = (C + CB - 1) / CB;
+        c0 = (int)(blockIdx.x % ncb) * CB;
+        bb = blockIdx.x / ncb;
+    }
+    const int band = bb % nbands;
+    const int b = bb / nbands;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lc = lane % LC, lq = lane / LC;
     const int th0 = band * R;
     const int rows_blk = min(R, nH - th0);
-    const long long plane = (long long)B * nH * nW * C;
-    const bool c_ok = c0 + lane < C;
-    for (int q = warp; q < rows_blk * nW; q += 8) {
+    const int CV = C / VEC;
+    const long long plane = (long long)B * nH * nW * CV;
+    const bool c_ok = c0 + VEC * lc < C;
+#pragma unroll 1
+    for (int q = warp * QW + lq; q < rows_blk * nW; q += 8 * QW) {
         const int br = q / nW, bw = q - br * nW;
-        float out[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-        if (c_ok) imtrans_bwd_block<float, MASK>(dV, Vm, plane, b, th0 + br, bw, nH, nW, C, c0 + lane, out);
+        T out[2][2];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) out[a][e] = zero_of(T());
+        if (c_ok)
+            imtrans_bwd_block<T, MASK>(reinterpret_cast<const T *>(dV), reinterpret_cast<const T *>(Vm), plane, b, th0 + br, bw, nH,
+                                       nW, CV, c0 / VEC + lc, out);
 #pragma unroll
         for (int a = 0; a < 2; ++a)
 #pragma unroll
             for (int e = 0; e < 2; ++e)
-                if (2 * bw + e < W) O[lane * pitch + (2 * br + a) * W + 2 * bw + e] = out[a][e];
+                if (2 * bw + e < W) {
+                    float *o = O + VEC * lc * pitch + (2 * br + a) * W + 2 * bw + e;
+                    put_lanes(o, pitch, out[a][e]);
+                }
     }
     __syncthreads();
     const int lo = 2 * th0, hi = min(2 * th0 + 2 * rows_blk, H);
     const int n = (hi - lo) * W;
-    for (int cc = warp; cc < 32; cc += 8) {
-        if (c0 + cc >= C) break;
-        float *dst = dX + (((long long)b * C + c0 + cc) * H + lo) * W;
-        const float *src = O + cc * pitch;
-        for (int i = lane; i < n; i += 32) dst[i] = src[i];
+    const int nch = min(CB, C - c0);
+    if (n == H * W) {
+        // the block's channels are one run of nch * H * W floats
+        float *dst = dX + ((long long)b * C + c0) * n;
+        for (int k = threadIdx.x; k < nch * n; k += 256) {
+            const int cc = k / n;
+            dst[k] = O[cc * pitch + (k - cc * n)];
+        }
+    } else {
+        for (int cc = warp; cc < nch; cc += 8) {
+            float *dst = dX + (((long long)b * C + c0 + cc) * H + lo) * W;
+            const float *src = O + cc * pitch;
+            for (int i = lane; i < n; i += 32) dst[i] = src[i];
+        }
     }
 }
 
@@ -433,23 +475,31 @@ int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W
         }
     } else {
         if (W <= 192) {
-            int R = kBandFloats / (2 * W);
+            // four channels per lane (16-byte loads) where the channels allow it and a band of 128 channels stays small
+            // four channels per lane (16-byte loads) where the channels allow it; 128 channels per block where a band of
+            // them stays below 50 KB (four blocks per SM), else 64
+            const bool vec = (C % 4 == 0) && C >= 64 && aligned16(dV) && (!Vm || aligned16(Vm)) && 2 * W <= kBandFloats / 2;
+            const bool wide = vec && C >= 128 && 2 * W <= kBandFloats / 4;
+            const int cb = wide ? 128 : (vec ? 64 : 32);
+            int R = (wide ? kBandFloats / 4 : (vec ? kBandFloats / 2 : kBandFloats)) / (2 * W);
             if (R < 1) R = 1;
             if (R > nH) R = nH;
             const int nbands = cdiv(nH, R);
+            R = cdiv(nH, nbands);                              // bands of even height
             const int pitch = (2 * R * W) | 1;
-            const int smem = 32 * pitch * (int)sizeof(float);
-            if ((long long)B * nbands > 0x7fffffffLL || cdiv(C, 32) > 65535) return WG2X2_ERR_UNSUPPORTED;
-            dim3 grid((unsigned)(B * nbands), cdiv(C, 32));
-            if (Vm) {
-                if (cudaFuncSetAttribute(imtrans_bwd_nchw_band_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                    return WG2X2_ERR_LAUNCH;
-                imtrans_bwd_nchw_band_kernel<true><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, R, nbands, pitch);
-            } else {
-                if (cudaFuncSetAttribute(imtrans_bwd_nchw_band_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                    return WG2X2_ERR_LAUNCH;
-                imtrans_bwd_nchw_band_kernel<false><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, R, nbands, pitch);
-            }
+            const int smem = cb * pitch * (int)sizeof(float);
+            if ((long long)B * nbands * cdiv(C, cb) > 0x7fffffffLL || cdiv(C, cb) > 65535) return WG2X2_ERR_UNSUPPORTED;
+            const dim3 grid = Vm ? dim3((unsigned)(B * nbands), cdiv(C, cb)) : dim3((unsigned)(B * nbands * cdiv(C, cb)));
+            auto launch = [&](auto kernel) -> bool {
+                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return false;
+                kernel<<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, R, nbands, pitch);
+                return true;
+            };
+            const bool launched =
+                wide ? (Vm ? launch(imtrans_bwd_nchw_band_kernel<4, 32, true>) : launch(imtrans_bwd_nchw_band_kernel<4, 32, false>))
+                : vec ? (Vm ? launch(imtrans_bwd_nchw_band_kernel<4, 16, true>) : launch(imtrans_bwd_nchw_band_kernel<4, 16, false>))
+                      : (Vm ? launch(imtrans_bwd_nchw_band_kernel<1, 32, true>) : launch(imtrans_bwd_nchw_band_kernel<1, 32, false>));
+            if (!launched) return WG2X2_ERR_LAUNCH;
             return launch_status();
         }
         const long long gx = (long long)B * nH * cdiv(nW, kTSEG);

@@ -131,6 +131,23 @@ def test_imtrans_bwd(wg, oracle, shape, use_mask, layout):
     _check(_from_layout(dX, layout), oracle.imtrans_bwd(dV, H, W, Vmask=V), what="imtrans_bwd")
 
 
+@pytest.mark.parametrize("use_mask", [False, True])
+@pytest.mark.parametrize("shape", [
+    (3, 7, 7, 132), (2, 13, 14, 256), (2, 40, 24, 128), (1, 31, 47, 192),     # 128 channels per block, several bands
+    (2, 9, 11, 68), (1, 27, 56, 64), (1, 30, 95, 72), (2, 20, 64, 128),       # 64 channels per block
+    (1, 12, 100, 64), (2, 6, 6, 130),                                          # scalar lanes (image too wide / C % 4 != 0)
+])
+def test_imtrans_bwd_nchw_channel_vector_paths(wg, oracle, shape, use_mask):
+    """The NCHW gather's 16-byte-load variants (and the shapes that fall back from them), odd sizes included."""
+    B, H, W, C = shape
+    rng = np.random.default_rng(23)
+    nH, nW = (H + 1) // 2, (W + 1) // 2
+    dV = rng.standard_normal((16, B, nH, nW, C)).astype(np.float32)
+    V = rng.standard_normal((16, B, nH, nW, C)).astype(np.float32) if use_mask else None
+    dX = wg.imtrans_bwd(_dev(dV), H, W, V_relu=_dev(V) if use_mask else None, layout="NCHW")
+    _check(_from_layout(dX, "NCHW"), oracle.imtrans_bwd(dV, H, W, Vmask=V), what="imtrans_bwd NCHW %s" % (shape,))
+
+
 def test_exhaustive_small_sizes(wg, oracle):
     """All H, W in 1..9 for a few channel counts, forward and backward, NHWC."""
     rng = np.random.default_rng(11)
