@@ -167,9 +167,11 @@ static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int
     const long long P = (long long)B * nH * nW;
     if (layout == WG2X2_NHWC) {
         conv_dm_nhwc_kernel<<<(unsigned)cdivll(P * (K / 4), 256), 256, 0, st>>>(dY, dM, P, nH, nW, H, W, K);
-    } else if (K % 4 == 0 && K >= 64 && 2 * W <= 192 && (reinterpret_cast<uintptr_t>(dM) & 15u) == 0) {
-        // four channels per lane; 128 channels per CTA where a band of them stays below 50 KB, else 64
-        const bool wide = K >= 128 && 2 * W <= 96;
+    } else if (K % 4 == 0 && K >= 64 && 2 * W <= 192 && (reinterpret_cast<uintptr_t>(dM) & 15u) == 0 &&
+               (long long)B * cdiv(nH, max(1, min(nH, 192 / (2 * W)))) * cdiv(K, 64) >= 4LL * kNumSMs) {
+        // four channels per lane (where that leaves four CTAs for every SM); 128 channels per CTA where a band of
+        // them stays below 50 KB and the CTAs still fill the GPU, else 64
+        const bool wide = K >= 128 && 2 * W <= 96 && (long long)B * cdiv(nH, max(1, min(nH, 96 / (2 * W)))) * cdiv(K, 128) >= 4LL * kNumSMs;
         const int cb = wide ? 128 : 64;
         int R = (wide ? 96 : 192) / (2 * W);
         if (R > nH) R = nH;

@@ -478,8 +478,12 @@ int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W
             // four channels per lane (16-byte loads) where the channels allow it and a band of 128 channels stays small
             // four channels per lane (16-byte loads) where the channels allow it; 128 channels per block where a band of
             // them stays below 50 KB (four blocks per SM), else 64
-            const bool vec = (C % 4 == 0) && C >= 64 && aligned16(dV) && (!Vm || aligned16(Vm)) && 2 * W <= kBandFloats / 2;
-            const bool wide = vec && C >= 128 && 2 * W <= kBandFloats / 4;
+            // -- and where that still leaves four CTAs for every SM (a small batch keeps the narrower blocks)
+            auto ctas = [&](int cbk, int band_floats) { return (long long)B * cdiv(nH, max(1, min(nH, band_floats / (2 * W)))) * cdiv(C, cbk); };
+            const long long fill = 4LL * kNumSMs;
+            const bool vec_ok = (C % 4 == 0) && C >= 64 && aligned16(dV) && (!Vm || aligned16(Vm)) && 2 * W <= kBandFloats / 2;
+            const bool wide = vec_ok && C >= 128 && 2 * W <= kBandFloats / 4 && ctas(128, kBandFloats / 4) >= fill;
+            const bool vec = wide || (vec_ok && ctas(64, kBandFloats / 2) >= fill);
             const int cb = wide ? 128 : (vec ? 64 : 32);
             int R = (wide ? kBandFloats / 4 : (vec ? kBandFloats / 2 : kBandFloats)) / (2 * W);
             if (R < 1) R = 1;
