@@ -93,8 +93,9 @@ __global__ void __launch_bounds__(256) conv_dm_nchw_kernel(const float *__restri
 }
 
 // The same with four channels per lane: 16-byte plane stores, 512 bytes per warp and store with LC = 32 lanes along
-// the channels (128 per CTA), 256 bytes with LC = 16 (64 per CTA, the two halves of a warp on two tiles at once).
-// Where the band is the whole image, the CTA's channels are one contiguous run of dY and are staged as such.
+// the channels (128 per CTA; LC = 16 would be 64 per CTA, the two halves of a warp on two tiles at once -- not used:
+// it measured slower than one channel per lane).  Where the band is the whole image, the CTA's channels are one
+// contiguous run of dY and are staged as such.
 template <int LC>
 __global__ void __launch_bounds__(256, 3) conv_dm_nchw_vec_kernel(const float *__restrict__ dY, float *__restrict__ dM, long long P, int nH,
                                                                     int nW, int H, int W, int K, int R, int nbands, int pitch)
@@ -167,29 +168,19 @@ static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int
     const long long P = (long long)B * nH * nW;
     if (layout == WG2X2_NHWC) {
         conv_dm_nhwc_kernel<<<(unsigned)cdivll(P * (K / 4), 256), 256, 0, st>>>(dY, dM, P, nH, nW, H, W, K);
-    } else if (K % 4 == 0 && K >= 64 && 2 * W <= 192 && (reinterpret_cast<uintptr_t>(dM) & 15u) == 0 &&
-               (long long)B * cdiv(nH, max(1, min(nH, 192 / (2 * W)))) * cdiv(K, 64) >= 4LL * kNumSMs) {
-        // four channels per lane (where that leaves four CTAs for every SM); 128 channels per CTA where a band of
-        // them stays below 50 KB and the CTAs still fill the GPU, else 64
-        const bool wide = K >= 128 && 2 * W <= 96 && (long long)B * cdiv(nH, max(1, min(nH, 96 / (2 * W)))) * cdiv(K, 128) >= 4LL * kNumSMs;
-        const int cb = wide ? 128 : 64;
-        int R = (wide ? 96 : 192) / (2 * W);
-        if (R > nH) R = nH;
-        const int nbands = cdiv(nH, R);
-        R = cdiv(nH, nbands);
+    } else if (K % 4 == 0 && K >= 128 && 2 * nH * W <= 96 && (reinterpret_cast<uintptr_t>(dM) & 15u) == 0 &&
+               (long long)B * cdiv(K, 128) >= 4LL * kNumSMs) {
+        // Four channels per lane, 128 per CTA, where the whole image is one small band and the CTAs fill the GPU
+        // (256 x 512 x 7 x 7: the backward step 193 against 197 us).  With several bands per image, or 64 channels
+        // per CTA, the one-channel-per-lane kernel below measured faster (144 against 161 us at 14 x 14).
+        const int R = nH, nbands = 1;
         const int pitch = (2 * R * W) | 1;
-        const int smem = cb * pitch * (int)sizeof(float);
-        if ((long long)B * nbands > 0x7fffffffLL || cdiv(K, cb) > 65535) return WG2X2_ERR_UNSUPPORTED;
-        const dim3 grid((unsigned)(B * nbands), cdiv(K, cb));
-        if (wide) {
-            if (cudaFuncSetAttribute(conv_dm_nchw_vec_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                return WG2X2_ERR_LAUNCH;
-            conv_dm_nchw_vec_kernel<32><<<grid, 256, smem, st>>>(dY, dM, P, nH, nW, H, W, K, R, nbands, pitch);
-        } else {
-            if (cudaFuncSetAttribute(conv_dm_nchw_vec_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-                return WG2X2_ERR_LAUNCH;
-            conv_dm_nchw_vec_kernel<16><<<grid, 256, smem, st>>>(dY, dM, P, nH, nW, H, W, K, R, nbands, pitch);
-        }
+        const int smem = 128 * pitch * (int)sizeof(float);
+        if ((long long)B > 0x7fffffffLL || cdiv(K, 128) > 65535) return WG2X2_ERR_UNSUPPORTED;
+        const dim3 grid((unsigned)B, cdiv(K, 128));
+        if (cudaFuncSetAttribute(conv_dm_nchw_vec_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return WG2X2_ERR_LAUNCH;
+        conv_dm_nchw_vec_kernel<32><<<grid, 256, smem, st>>>(dY, dM, P, nH, nW, H, W, K, R, nbands, pitch);
     } else {
         int R = 384 / (2 * W);
         if (R < 1) R = 1;

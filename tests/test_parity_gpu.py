@@ -131,21 +131,41 @@ def test_imtrans_bwd(wg, oracle, shape, use_mask, layout):
     _check(_from_layout(dX, layout), oracle.imtrans_bwd(dV, H, W, Vmask=V), what="imtrans_bwd")
 
 
+# The NCHW transform kernels with four channels per lane are chosen only where their grid fills the GPU (at least
+# four CTAs per SM), so these shapes are sized to select them: 128 channels per CTA in bands, 128 per CTA with the
+# whole image as one band, 64 per CTA (image too wide for 128), 64 per CTA with a ragged last block.
+_VEC_BWD = [(40, 13, 14, 640), (150, 7, 7, 512), (16, 27, 56, 192), (150, 13, 14, 100)]
+_VEC_FWD = [(150, 7, 7, 512), (160, 5, 8, 388), (30, 13, 14, 640), (150, 13, 14, 100)]   # the first two take the 128-channel kernel
+
+
 @pytest.mark.parametrize("use_mask", [False, True])
-@pytest.mark.parametrize("shape", [
-    (3, 7, 7, 132), (2, 13, 14, 256), (2, 40, 24, 128), (1, 31, 47, 192),     # 128 channels per block, several bands
-    (2, 9, 11, 68), (1, 27, 56, 64), (1, 30, 95, 72), (2, 20, 64, 128),       # 64 channels per block
-    (1, 12, 100, 64), (2, 6, 6, 130),                                          # scalar lanes (image too wide / C % 4 != 0)
-])
+@pytest.mark.parametrize("shape", _VEC_BWD + [(3, 7, 7, 132), (2, 9, 11, 68), (1, 12, 100, 64), (2, 6, 6, 130)])
 def test_imtrans_bwd_nchw_channel_vector_paths(wg, oracle, shape, use_mask):
-    """The NCHW gather's 16-byte-load variants (and the shapes that fall back from them), odd sizes included."""
+    """The NCHW gather's 16-byte-load variants (and small shapes that fall back from them), odd sizes included."""
     B, H, W, C = shape
     rng = np.random.default_rng(23)
     nH, nW = (H + 1) // 2, (W + 1) // 2
-    dV = rng.standard_normal((16, B, nH, nW, C)).astype(np.float32)
-    V = rng.standard_normal((16, B, nH, nW, C)).astype(np.float32) if use_mask else None
+    dV = rng.standard_normal((16, B, nH, nW, C), dtype=np.float32)
+    V = rng.standard_normal((16, B, nH, nW, C), dtype=np.float32) if use_mask else None
     dX = wg.imtrans_bwd(_dev(dV), H, W, V_relu=_dev(V) if use_mask else None, layout="NCHW")
-    _check(_from_layout(dX, "NCHW"), oracle.imtrans_bwd(dV, H, W, Vmask=V), what="imtrans_bwd NCHW %s" % (shape,))
+    _check(_from_layout(dX, "NCHW"), oracle.imtrans_bwd(dV, H, W, Vmask=V, dtype=np.float32), what="imtrans_bwd NCHW %s" % (shape,))
+
+
+@pytest.mark.parametrize("affine", [False, True])
+@pytest.mark.parametrize("shape", _VEC_FWD + [(3, 7, 7, 132), (2, 9, 11, 68), (2, 6, 6, 130)])
+def test_imtrans_fwd_nchw_channel_vector_paths(wg, oracle, shape, affine):
+    """The NCHW input transform's 16-byte-store variants, with and without the folded per-channel affine map and ReLU."""
+    B, H, W, C = shape
+    rng = np.random.default_rng(29)
+    X = rng.standard_normal((B, H, W, C), dtype=np.float32)
+    kw, Xo = {}, X
+    if affine:
+        s_in, b_in = (1 + 0.2 * rng.standard_normal(C)).astype(np.float32), (0.3 * rng.standard_normal(C)).astype(np.float32)
+        kw = dict(in_scale=_dev(s_in), in_shift=_dev(b_in))
+        Xo = X.astype(np.float64) * s_in + b_in
+    for relu in (True, False):
+        V = wg.imtrans_fwd(_dev(_to_layout(X, "NCHW")), relu=relu, layout="NCHW", **kw).cpu().numpy()
+        _check(V, oracle.imtrans_fwd(Xo, relu=relu), what="imtrans_fwd NCHW %s relu=%s" % (shape, relu))
 
 
 def test_exhaustive_small_sizes(wg, oracle):
