@@ -1,17 +1,24 @@
 #!/usr/bin/env python
-"""Benchmark of the Winograd-ReLU F(2x2,3x3) convolution layer forward (transform + ReLU -> 16 products
--> output transform) on B200, one process per GPU, batch-sharded (weak scaling, no collective on the path).
+"""Benchmark of the Winograd-ReLU F(2x2,3x3) convolution path on B200, one process per GPU.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--math tf32|fp32]
-                    [--workload cfg2|cfg1|cfg3] [--layout NCHW|NHWC]
+                    [--workload cfg2|cfg1|cfg3|cfg4|cfg5] [--layout NCHW|NHWC] [--only-headline]
 
-Prints ONE JSON line (rank 0).  `value` is images per second through the layer with inputs resident in
-HBM; `e2e` is the same through the public call with host buffers (H2D of X and D2H of Y inside the timed
-region); `roofline` describes the dominant kernel; `cpu_baseline` is the CPU oracle on the host cores.
-`--impl reference` times the reference layer math on the host cores (the reference has no CPU
-implementation of its own -- its CPU kernels exit -- so this is the C restatement under oracle/).
+Prints ONE JSON line (rank 0).  The headline (`value`, `ms_per_step`, `roofline`, `e2e`) is the layer forward
+of the conv2_x-shaped workload (N=64, C=K=64, 56x56, dense): `value` with inputs resident in HBM, timed over
+`--steps` launches back to back between two CUDA events; `e2e` the same through the host-buffer call (H2D of
+X and D2H of Y inside the timed region); `roofline` for the dominant kernel, whose duration comes from a
+separate short pass after the timed region.  `configs` holds one sub-record per other workload, each measured
+in this run with its own step count: cfg1 (N=4 layer), cfg3 (pruned conv4_x-shaped layer forward, with the
+zero-block skip rate of its mask), cfg5 (conv5_x-shaped layer backward on the tensor cores) and cfg4
+(ResNet-18-var forward, batch 256 in total: sharded over the ranks under --gpus N, replayed as a CUDA graph,
+with the NCCL all-gather of the logits timed beside it).  `cpu_baseline` is the C restatement of the layer
+math on the host cores; `reference_gpu` is the reference's own CUDA kernels (compiled unmodified for sm_100a
+by oracle/Makefile) on the headline workload.  `--impl reference` times the C restatement (the reference has
+no CPU implementation of its own: its CPU kernels exit).
 """
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -30,8 +37,17 @@ WORKLOADS = {  # per-GPU shapes: B, C, K, H, W, weight density, post-ReLU input
     "cfg2": dict(B=64, C=64, K=64, H=56, W=56, density=1.0, halfnormal=False),
     "cfg3": dict(B=128, C=256, K=256, H=14, W=14, density=0.3, halfnormal=True),
 }
+CFG5 = dict(B=256, C=512, K=512, H=7, W=7, density=0.2)
 METRIC = "winograd_relu_conv_layer_fwd_throughput"
 UNIT = "img/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the one-pass ncu captures summarised under
+# profiles/ (taken at the workload's full size); a constant from those captures, not a per-run measurement
+NCU_TRAFFIC = {
+    ("cfg2", 64, "NCHW", "imtrans"): (197.8e6, "ncu capture, profiles/imtrans_fwd_nchw_band_kernel_cfg2.md"),
+    ("cfg2", 64, "NCHW", "conv"): (224.7e6, "ncu capture, profiles/conv_fwd_tc_kernel_cfg2.md"),
+    ("cfg2", 64, "NCHW", "fused"): (60.0e6, "ncu capture, profiles/layer_fwd_fused_kernel_cfg2.md (X read once; most of Y is still "
+                                            "dirty in L2 when the launch ends, so it is below the algorithmic X + W + Y)"),
+}
 
 
 def peaks():
@@ -55,7 +71,7 @@ def make_inputs(wl, seed=1):
 
 
 class ClockSampler:
-    """`nvidia-smi -lms 50` running beside the benchmark; rows are stamped on arrival so that the ones that
+    """`nvidia-smi -lms 20` running beside the benchmark; rows are stamped on arrival so that the ones that
     fall inside the timed region can be picked out afterwards."""
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
@@ -94,151 +110,376 @@ class ClockSampler:
                     reasons=reasons, samples=len(inside), window=window)
 
 
-def cpu_oracle_rate(wl, layout_unused, seconds=12.0, sample_b=None):
-    """Images per second of the C oracle (float32, OpenMP over all host cores) on a batch slice."""
+# ---------------------------------------------------------------------------------------------------------
+# CPU legs (the only places where this file runs anything under oracle/)
+# ---------------------------------------------------------------------------------------------------------
+def _fwd_port(wl, b):
+    """A callable that runs the C restatement of the layer forward once on a batch slice of b images."""
     from oracle import wg_oracle as o
-    cores = o.set_threads()
-    b = sample_b or max(1, min(wl["B"], 4))
     X, Wt = make_inputs(dict(wl, B=b))
     Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
     P = b * ((wl["H"] + 1) // 2) * ((wl["W"] + 1) // 2)
     bufs = (np.empty((b, wl["H"], wl["W"], wl["K"]), np.float32), np.empty(16 * P * wl["C"], np.float32),
             np.empty(16 * P * wl["K"], np.float32))
-    o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)  # warm
+    return lambda: o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+
+
+def _bwd_port(b):
+    """The C restatement of the conv5_x-shaped backward (wgo_conv_bwd + wgo_imtrans_bwd with the ReLU mask) on b images."""
+    from oracle import wg_oracle as o
+    C, K, H, W = CFG5["C"], CFG5["K"], CFG5["H"], CFG5["W"]
+    rng = np.random.default_rng(1)
+    X = rng.standard_normal((b, H, W, C), dtype=np.float32)
+    mask = (np.random.default_rng(3).random((16, C, K)) < CFG5["density"]).astype(np.float32)
+    Wt = (0.05 * np.random.default_rng(2).standard_normal((16, C, K))).astype(np.float32) * mask
+    dY = rng.standard_normal((b, H, W, K), dtype=np.float32)
+    V = o.imtrans_fwd(X, relu=True, dtype=np.float32)
+
+    def run():
+        dV, dW = o.conv_bwd(V, Wt, dY, mask=mask, dtype=np.float32)
+        return o.imtrans_bwd(dV, H, W, Vmask=V, dtype=np.float32), dW
+    return run
+
+
+def _time_cpu(fn, seconds):
+    fn()   # warm
     n, t0 = 0, time.perf_counter()
     while True:
-        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+        fn()
         n += 1
         dt = time.perf_counter() - t0
         if dt > seconds:
-            break
+            return n, dt
+
+
+def cpu_baseline(wl, seconds=10.0):
+    """Images per second of the C restatement (float32, OpenMP over all host cores) on a batch slice."""
+    from oracle import wg_oracle as o
+    cores = o.set_threads()
+    b = max(1, min(wl["B"], 4))
+    n, dt = _time_cpu(_fwd_port(wl, b), seconds)
     return dict(value=b * n / dt, unit=UNIT, cores=cores, kind="port",
-                sample="batch slice of %d images of the %dx%dx%dx%d layer, %d passes in %.1f s, float32 C restatement with OpenMP"
-                       % (b, wl["C"], wl["K"], wl["H"], wl["W"], n, dt)), b, dt / n
+                sample="batch slice of %d images of the %dx%dx%dx%d layer forward, %d passes in %.1f s, float32 C restatement with OpenMP"
+                       % (b, wl["C"], wl["K"], wl["H"], wl["W"], n, dt))
 
 
-def run_reference(args, wl, rank, world):
+def cpu_baseline_bwd(seconds=6.0):
+    from oracle import wg_oracle as o
+    cores = o.set_threads()
+    b = 4
+    n, dt = _time_cpu(_bwd_port(b), seconds)
+    return dict(value=b * n / dt, unit=UNIT, cores=cores, kind="port",
+                sample="batch slice of %d images of the 512x512x7x7 layer backward (dV, masked dW, dX with the ReLU mask), %d passes in "
+                       "%.1f s, float32 C restatement with OpenMP" % (b, n, dt))
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference layer math on the host cores.  The reference ships GPU-only ops (its CPU
+    kernels print and exit), so this arm is the C restatement under oracle/ on a bounded batch slice."""
     if rank != 0:
         return
     from oracle import wg_oracle as o
     cores = o.set_threads()
-    b = max(1, min(wl["B"], 4))
-    X, Wt = make_inputs(dict(wl, B=b))
-    Xn = np.ascontiguousarray(np.transpose(X, (0, 2, 3, 1)))
-    P = b * ((wl["H"] + 1) // 2) * ((wl["W"] + 1) // 2)
-    bufs = (np.empty((b, wl["H"], wl["W"], wl["K"]), np.float32), np.empty(16 * P * wl["C"], np.float32),
-            np.empty(16 * P * wl["K"], np.float32))
+    if args.workload == "cfg4":
+        # the network's 16 Winograd-ReLU layers, one image each, summed (the dense parts of the network -- stem, pools,
+        # 1x1 shortcuts, FC -- are stock ops in the reference too and are left out)
+        shapes = [(64, 64, 56, 4), (64, 128, 28, 1), (128, 128, 28, 3), (128, 256, 14, 1), (256, 256, 14, 3),
+                  (256, 512, 7, 1), (512, 512, 7, 3)]
+        fns = [(_fwd_port(dict(C=c, K=k, H=s, W=s, density=1.0, halfnormal=False), 1), rep) for c, k, s, rep in shapes]
+        b, metric = 1, "resnet18_var_forward_throughput"
+        step = lambda: [f() for f, rep in fns for _ in range(rep)]
+        sample = "each step = the 16 Winograd-ReLU layers of the network on one image (host cores, OpenMP, float32); dense layers left out"
+        cfg = {"workload": "cfg4", "sample_batch": 1}
+    elif args.workload == "cfg5":
+        b, metric = 4, "winograd_relu_conv_layer_bwd_throughput"
+        step = _bwd_port(b)
+        sample = "each step = batch slice of %d images of the backward workload (host cores, OpenMP, float32)" % b
+        cfg = {"workload": "cfg5", "layer": CFG5, "layout": "NHWC", "sample_batch": b}
+    else:
+        wl = dict(WORKLOADS[args.workload])
+        b, metric = max(1, min(wl["B"], 4)), METRIC
+        step = _fwd_port(wl, b)
+        sample = "each step = batch slice of %d images of the workload (host cores, OpenMP, float32)" % b
+        cfg = {"workload": args.workload, "layer": wl, "layout": "NHWC", "sample_batch": b}
     for _ in range(args.warmup):
-        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        o.layer_fwd(Xn, Wt, relu=True, dtype=np.float32, bufs=bufs)
+        step()
     dt = time.perf_counter() - t0
     val = b * args.steps / dt
-    sample = "each step = batch slice of %d images of the workload (host cores, OpenMP, float32)" % b
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "layer": wl, "layout": "NHWC", "sample_batch": b},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "impl": "reference", "metric": metric, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "cfg4" else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": cfg, "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference ships GPU-only ops (its CPU kernels exit); this arm is the C restatement of its layer math",
     }))
 
 
-def run_backward(args, rank, world, local):
-    """Backward workload (cfg5): backward of a pruned conv5_x-shaped layer (N=256, C=K=512, 7x7, density 0.2):
-    dX through the transposed products plus the input-transform gradient (ReLU mask applied), and the
-    masked dW.  Per-GPU batch fixed (weak scaling); dW would need one all-reduce when sharded, which is
-    reported separately and not part of the step."""
-    import torch
-    import torch.distributed as dist
-    import wg2x2
+# ---------------------------------------------------------------------------------------------------------
+# GPU helpers
+# ---------------------------------------------------------------------------------------------------------
+class Ctx:
+    """Rank, device and the collective plumbing shared by the GPU workloads."""
 
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, C, K, H, W = (args.batch if args.batch > 0 else 256), 512, 512, 7, 7
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+
+    def max_over_ranks(self, ms):
+        if self.world == 1:
+            return float(ms)
+        t = self.torch.tensor([ms], device=self.dev, dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+def timed(ctx, fn, steps, warmup=3):
+    """ms per call of fn(i): `warmup` untimed calls, then `steps` calls back to back between two CUDA events on the
+    launching stream, barrier + synchronize on both sides, max over ranks."""
+    torch = ctx.torch
+    for i in range(warmup):
+        fn(i)
+    ctx.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        fn(i)
+    b.record()
+    ctx.barrier()
+    return ctx.max_over_ranks(a.elapsed_time(b)) / steps
+
+
+def each_launch_ms(torch, fn, n):
+    """Mean duration of fn(i) with every call bracketed by its own pair of events (no overlap with its neighbours)."""
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for i in range(n):
+        ev[i][0].record()
+        fn(i)
+        ev[i][1].record()
+    torch.cuda.synchronize()
+    return float(np.mean([a.elapsed_time(b) for a, b in ev]))
+
+
+def check_status(wg2x2):
+    status, where = wg2x2.last_device_status()
+    if status != 0:
+        raise RuntimeError("device status %d at 0x%x" % (status, where))
+
+
+class LayerFwd:
+    """One Winograd-ReLU layer forward on rotating input buffers (inputs + outputs of consecutive steps exceed L2)."""
+
+    def __init__(self, ctx, wl, layout, math, path, nbuf=4):
+        import wg2x2
+        torch = ctx.torch
+        self.wg, self.ctx, self.wl, self.layout, self.math = wg2x2, ctx, wl, layout, math
+        B, C, K, H, W = wl["B"], wl["C"], wl["K"], wl["H"], wl["W"]
+        nH, nW = (H + 1) // 2, (W + 1) // 2
+        self.P = B * nH * nW
+        Xh, Wth = make_inputs(wl, seed=1 + ctx.rank)
+        if layout == "NHWC":
+            Xh = np.ascontiguousarray(np.transpose(Xh, (0, 2, 3, 1)))
+        self.Xh, self.Wth = Xh, Wth
+        # enough rotating inputs that what a step touches has left L2 (126 MB) when its buffer comes round again
+        while nbuf * Xh.nbytes < 200e6 and nbuf < 16:
+            nbuf += 1
+        self.nbuf = nbuf
+        self.Xs = [torch.from_numpy(Xh).to(ctx.dev) + 0.0 * i for i in range(nbuf)]
+        self.Wt = torch.from_numpy(Wth).to(ctx.dev)
+        self.V = torch.empty((16, B, nH, nW, C), device=ctx.dev)
+        self.Y = torch.empty((B, K, H, W) if layout == "NCHW" else (B, H, W, K), device=ctx.dev)
+        lib = wg2x2._lib.lib
+        ws_n = lib.wg2x2_conv_fwd_workspace_bytes(B, nH, nW, C, K, wg2x2.ops._MATHS[math])
+        self.ws = torch.empty(max(ws_n, 1), dtype=torch.uint8, device=ctx.dev)
+        # the weights do not change between forward passes: the tensor-core path repacks them once
+        self.prepared = wg2x2.prepare_weights(self.Wt) if math == "tf32" else None
+        cws_n = lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, nH, nW, C, K) if self.prepared is not None else 0
+        self.cws = torch.empty(cws_n, dtype=torch.uint8, device=ctx.dev) if cws_n else None   # products of the wide path (C, K >= 256)
+        fused_ok = self.prepared is not None and layout == "NCHW" and wg2x2.fused_supported(B, H, W, C, K, "NCHW")
+        fused_pays = K <= 128 or (K <= 256 and C <= 64)          # the library's own rule (wg2x2_layer_fwd_prepared)
+        self.use_fused = fused_ok and (path == "fused" or (path == "auto" and fused_pays))
+        self.bytesX, self.bytesV, self.bytesY, self.bytesW = 4 * B * C * H * W, 64 * self.P * C, 4 * B * K * H * W, 64 * C * K
+        self.flops = 2.0 * 16 * self.P * C * K
+
+    def imtrans(self, i):
+        self.wg.imtrans_fwd(self.Xs[i % self.nbuf], relu=True, layout=self.layout, out=self.V)
+
+    def conv(self, i):
+        wl = self.wl
+        if self.prepared is not None:
+            self.wg.conv_fwd_prepared(self.V, self.prepared, wl["K"], wl["H"], wl["W"], layout=self.layout, out=self.Y, workspace=self.cws)
+        else:
+            self.wg.conv_fwd(self.V, self.Wt, wl["H"], wl["W"], layout=self.layout, math=self.math, out=self.Y, workspace=self.ws)
+
+    def fused(self, i):
+        self.wg.layer_fwd_fused(self.Xs[i % self.nbuf], self.prepared, self.wl["K"], relu=True, out=self.Y)
+
+    def step(self, i):
+        if self.use_fused:
+            self.fused(i)
+        else:
+            self.imtrans(i)
+            self.conv(i)
+
+    def layer_bytes(self):
+        return self.bytesX + self.bytesW + self.bytesY if self.use_fused else 2 * self.bytesV + self.bytesX + self.bytesW + self.bytesY
+
+    def roofline(self, pk, n_each=24):
+        """Per-kernel durations from a separate pass (each launch bracketed by its own events) and the roofline of
+        the dominant kernel: algorithmic bytes or flops of one launch / its duration, against the measured peak."""
+        torch = self.ctx.torch
+        tf32_peak = pk["bf16_tflops"] / 2.0
+        k1_bytes, k2_bytes = self.bytesX + self.bytesV, self.bytesV + self.bytesW + self.bytesY
+        if self.use_fused:
+            ms = each_launch_ms(torch, self.fused, n_each)
+            fb = self.bytesX + self.bytesW + self.bytesY
+            roof = dict(kernel="layer_fwd_fused_kernel (transform + ReLU + products + output transform, one launch = the whole layer)",
+                        bound="hbm", achieved=fb / (ms * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"],
+                        algorithmic_bytes=fb, tensor_tflops_algorithmic=self.flops / (ms * 1e-3) / 1e12,
+                        tensor_tflops_issued=2.25 * self.flops / (ms * 1e-3) / 1e12, kernels_ms={"layer_fwd_fused": ms},
+                        note="only X, W and Y cross HBM; the kernel is paced by the SM, not by HBM (36 signed MMAs per 8 channels instead "
+                             "of 16, transform warps in step with them).  kernels_ms is a launch bracketed by events on its own; back to "
+                             "back the launches overlap their neighbours' tails (programmatic dependent launch), so ms_per_step can be below it")
+            which = "fused"
+        else:
+            ms1 = each_launch_ms(torch, self.imtrans, n_each)
+            ms2 = each_launch_ms(torch, self.conv, n_each)
+            t_hbm, t_tensor = k2_bytes / (pk["hbm_gbs"] * 1e9), self.flops / (tf32_peak * 1e12)
+            if ms2 >= ms1:
+                which = "conv"
+                if self.math == "tf32" and t_tensor > t_hbm:
+                    roof = dict(kernel="conv_fwd (the 16 products + output transform)", bound="tensor", achieved=self.flops / (ms2 * 1e-3) / 1e12,
+                                peak=tf32_peak, unit="TFLOP/s", peak_source=pk["source"] + " bf16 / 2", algorithmic_flops=self.flops)
+                else:
+                    roof = dict(kernel="conv_fwd (the 16 products + output transform)", bound="hbm", achieved=k2_bytes / (ms2 * 1e-3) / 1e9,
+                                peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"], algorithmic_bytes=k2_bytes)
+            else:
+                which = "imtrans"
+                roof = dict(kernel="imtrans_fwd (input transform + ReLU)", bound="hbm", achieved=k1_bytes / (ms1 * 1e-3) / 1e9,
+                            peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"], algorithmic_bytes=k1_bytes)
+            roof["kernels_ms"] = {"imtrans_fwd": ms1, "conv_fwd": ms2}
+            roof["imtrans_fwd_gbs"] = k1_bytes / (ms1 * 1e-3) / 1e9
+            roof["conv_fwd_gbs"] = k2_bytes / (ms2 * 1e-3) / 1e9
+            roof["conv_fwd_tflops"] = self.flops / (ms2 * 1e-3) / 1e12
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        return roof, which
+
+
+def sub_layer_fwd(ctx, name, args, steps):
+    """configs.<name>: one layer forward workload, device-resident."""
+    wl = dict(WORKLOADS[name])
+    L = LayerFwd(ctx, wl, "NCHW", "tf32", "auto")
+    ms = timed(ctx, L.step, steps)
+    check_status(L.wg)
+    pk = peaks()
+    roof, _ = L.roofline(pk, n_each=12)
+    roof["traffic"] = None
+    rec = {"ms_per_step": ms, "steps": steps, "img_s": ctx.world * wl["B"] / (ms * 1e-3), "layer": wl, "layout": "NCHW", "dtype": "tf32",
+           "path": "one fused kernel" if L.use_fused else ("input transform, then products as GEMMs with 256 output channels per unit "
+                                                          "into scratch + output transform pass" if L.cws is not None else "two kernels, V through HBM"),
+           "layer_tflops": L.flops / (ms * 1e-3) / 1e12, "layer_gbs": L.layer_bytes() / (ms * 1e-3) / 1e9,
+           "strict_layer_bound_ms": 1e3 * max((L.bytesX + L.bytesW + L.bytesY) / (pk["hbm_gbs"] * 1e9), L.flops / (pk["bf16_tflops"] / 2 * 1e12)),
+           "roofline": roof}
+    if wl["density"] < 1.0:
+        from wg_weights import gen_prune_mask, zero_block_fraction
+        rec["skip_rate"] = zero_block_fraction(L.Wth)           # share of 64 x 32 weight blocks that are all zero and skipped
+        w2 = (0.05 * np.random.default_rng(2).standard_normal((16, wl["C"], wl["K"]))).astype(np.float32)
+        rec["skip_rate_magnitude_mask"] = zero_block_fraction(gen_prune_mask(w2, wl["density"]))   # the reference's top-|w| mask, same density
+        rec["skip_note"] = "unstructured masks leave no 64 x 32 block empty: tensor-pipe figures are from dense flops"
+    del L
+    ctx.torch.cuda.empty_cache()
+    return rec
+
+
+def sub_backward(ctx, args, steps, math="tf32", batch=0):
+    """configs.cfg5: backward of the pruned conv5_x-shaped layer: dV and masked dW (gradient products), then dX through the
+    input-transform gradient with the ReLU mask.  Per-GPU batch fixed."""
+    import wg2x2
+    torch = ctx.torch
+    B, C, K, H, W = (batch or CFG5["B"]), CFG5["C"], CFG5["K"], CFG5["H"], CFG5["W"]
     nH = nW = 4
     P = B * nH * nW
-    g = torch.Generator().manual_seed(1 + rank)
-    X = torch.randn((B, C, H, W), generator=g).to(dev)
-    mask = (torch.rand((16, C, K), generator=torch.Generator().manual_seed(3)) < 0.2).float().to(dev)
-    Wt = (0.05 * torch.randn((16, C, K), generator=torch.Generator().manual_seed(2))).to(dev) * mask
-    dYs = [torch.randn((B, K, H, W), generator=g).to(dev) for _ in range(2)]
+    g = torch.Generator().manual_seed(1 + ctx.rank)
+    X = torch.randn((B, C, H, W), generator=g).to(ctx.dev)
+    mask = (torch.rand((16, C, K), generator=torch.Generator().manual_seed(3)) < CFG5["density"]).float().to(ctx.dev)
+    Wt = (0.05 * torch.randn((16, C, K), generator=torch.Generator().manual_seed(2))).to(ctx.dev) * mask
+    dYs = [torch.randn((B, K, H, W), generator=g).to(ctx.dev) for _ in range(2)]
     V = wg2x2.imtrans_fwd(X, relu=True, layout="NCHW")
+    hold = {}
+
+    def products(i):
+        hold["dV"], hold["dW"] = wg2x2.conv_bwd(V, Wt, dYs[i % 2], mask=mask, layout="NCHW", relu=False, math=math)
+
+    def gather(i):
+        hold["dX"] = wg2x2.imtrans_bwd(hold["dV"], H, W, V_relu=V, layout="NCHW")   # ReLU mask applied inside the gather
 
     def step(i):
-        dV, dW = wg2x2.conv_bwd(V, Wt, dYs[i % 2], mask=mask, layout="NCHW", relu=False, math=args.bwd_math)
-        dX = wg2x2.imtrans_bwd(dV, H, W, V_relu=V, layout="NCHW")   # ReLU mask applied inside the gather
-        return dX, dW
+        products(i)
+        gather(i)
 
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    wall0 = time.time()
-    a.record()
-    for i in range(args.steps):
-        step(i)
-    b.record()
-    torch.cuda.synchronize()
-    clocks = sampler.finish(wall0, time.time())
-    t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.barrier()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
-    if rank == 0:
-        pk = peaks()
-        flops = 2.0 * 2 * 16 * P * C * K
-        bytes_alg = 4.0 * B * K * H * W + 64.0 * P * C + 2 * 64.0 * C * K + 4.0 * B * C * H * W + 64.0 * C * K
-        print(json.dumps({
-            "metric": "winograd_relu_conv_layer_bwd_throughput", "value": world * B / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "tf32" if args.bwd_math == "tf32" else "f32", "data": "synthetic",
-            "config": {"workload": "cfg5", "layer": dict(B=B, C=C, K=K, H=H, W=W, density=0.2), "layout": "NCHW",
-                       "l2": "two rotating dY buffers; V (%.0f MB) and dV exceed L2" % (64.0 * P * C / 1e6)},
-            "layer_tflops": flops * world / (ms * 1e-3) / 1e12,
-            "roofline": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": pk["bf16_tflops"] / 2, "unit": "TFLOP/s",
-                         "frac": flops / (ms * 1e-3) / 1e12 / (pk["bf16_tflops"] / 2), "traffic": None,
-                         "algorithmic_bytes": bytes_alg, "peak_source": pk["source"] + " bf16 / 2"},
-            "clocks": clocks, "gpu_launches": args.steps * 4,
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+    ms = timed(ctx, step, steps)
+    check_status(wg2x2)
+    ms_p = each_launch_ms(torch, products, 6)
+    ms_g = each_launch_ms(torch, gather, 6)
+    pk = peaks()
+    flops = 2.0 * 2 * 16 * P * C * K
+    bytes_alg = 4.0 * B * K * H * W + 64.0 * P * C + 2 * 64.0 * C * K + 4.0 * B * C * H * W + 64.0 * C * K
+    tf32_peak = pk["bf16_tflops"] / 2
+    from wg_weights import zero_block_fraction
+    rec = {"ms_per_step": ms, "steps": steps, "img_s": ctx.world * B / (ms * 1e-3), "layer": dict(CFG5, B=B), "layout": "NCHW",
+           "dtype": "tf32" if math == "tf32" else "f32", "layer_tflops": flops / (ms * 1e-3) / 1e12,
+           "strict_layer_bound_ms": 1e3 * max(bytes_alg / (pk["hbm_gbs"] * 1e9), flops / (tf32_peak * 1e12)),
+           "skip_rate": zero_block_fraction(mask.cpu().numpy()),
+           "roofline": {"kernel": "conv_bwd (A dY A^T, dV = dM.W^T, dW = V^T.dM on the tensor cores) + imtrans_bwd (B g B^T gather with the ReLU mask)",
+                        "bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": tf32_peak, "unit": "TFLOP/s",
+                        "frac": flops / (ms * 1e-3) / 1e12 / tf32_peak, "traffic": None, "algorithmic_flops": flops,
+                        "algorithmic_bytes": bytes_alg, "peak_source": pk["source"] + " bf16 / 2",
+                        "kernels_ms": {"conv_bwd": ms_p, "imtrans_bwd": ms_g},
+                        "conv_bwd_tflops": flops / (ms_p * 1e-3) / 1e12,
+                        "imtrans_bwd_gbs": (2 * 64.0 * P * C + 4.0 * B * C * H * W) / (ms_g * 1e-3) / 1e9}}
+    del X, V, dYs, hold
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_resnet(args, rank, world, local):
-    """Network workload (cfg4): ResNet-18-var forward, batch 256 in total, sharded over the ranks (strong scaling)."""
-    import torch
-    import torch.distributed as dist
-    import wg2x2  # noqa: F401
+def sub_resnet(ctx, args, steps, total=256):
+    """configs.cfg4: ResNet-18-var forward, `total` images sharded over the ranks (strong scaling), replayed as a CUDA graph;
+    under more than one rank the NCCL all-gather of the logits is timed beside it."""
+    import wg2x2
     from resnet18_var import ResNet18Var
-
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    total = args.batch if args.batch > 0 else 256
-    lo, hi = wg2x2.shard.shard_range(total, world, rank)
+    torch = ctx.torch
+    lo, hi = wg2x2.shard.shard_range(total, ctx.world, ctx.rank)
     n = hi - lo
-    model = ResNet18Var(stage5_pool=not args.stage5_at_14, math=args.math, layout=args.net_layout).to(dev).eval()
-    gen = torch.Generator().manual_seed(100 + rank)
+    model = ResNet18Var(stage5_pool=not args.stage5_at_14, math=args.math, layout=args.net_layout).to(ctx.dev).eval()
+    gen = torch.Generator().manual_seed(100 + ctx.rank)
     imgs_h = torch.randn((n, 3, 224, 224), generator=gen).pin_memory()
-    imgs = [imgs_h.to(dev) + 0.0 * i for i in range(2)]
+    imgs = [imgs_h.to(ctx.dev) + 0.0 * i for i in range(2)]
     with torch.no_grad():
-        for i in range(args.warmup):
+        for i in range(2):
             model(imgs[i % 2])
         torch.cuda.synchronize()
-        # the forward pass is a fixed sequence of ~150 launches: capture it once per input buffer and replay
-        graphs = None
-        if not args.no_graph:
+        graphs, outs = None, None
+        if not args.no_graph:     # the forward pass is a fixed sequence of ~150 launches: capture it once per input buffer and replay
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             graphs, outs = [], []
@@ -249,38 +490,33 @@ def run_resnet(args, rank, world, local):
                         outs.append(model(imgs[k]))
                     graphs.append(g)
             torch.cuda.current_stream().wait_stream(side)
-            for k in range(2):
-                graphs[k].replay()
-            torch.cuda.synchronize()
+        last = {}
 
         def fwd(i):
             if graphs is not None:
                 graphs[i % 2].replay()
+                last["y"] = outs[i % 2]
             else:
-                model(imgs[i % 2])
+                last["y"] = model(imgs[i % 2])
 
-        if world > 1:
-            dist.barrier()
-        sampler = ClockSampler(local)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        wall0 = time.time()
-        a.record()
-        for i in range(args.steps):
-            fwd(i)
-        b.record()
-        torch.cuda.synchronize()
-        clocks = sampler.finish(wall0, time.time())
-        t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.barrier()
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item()) / args.steps
+        ms = timed(ctx, fwd, steps, warmup=2)
+        check_status(wg2x2)
+        rec = {"ms_per_step": ms, "steps": steps, "img_s": total / (ms * 1e-3), "scaling": "strong", "total_batch": total, "per_gpu_batch": n,
+               "image": 224, "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": args.net_layout, "dtype": "tf32" if args.math == "tf32" else "f32",
+               "launch": "eager" if graphs is None else "one CUDA graph per input buffer, replayed",
+               "winograd_tflops_dense": model.winograd_flops(total) / (ms * 1e-3) / 1e12,
+               "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; stem, pools, 1x1 shortcuts, FC on stock torch"}
+        if ctx.world > 1:      # the one collective of the sharded forward: every rank receives all logits (not on the timed path above)
+            gm = timed(ctx, lambda i: wg2x2.shard.gather_batch(last["y"], total), 10, warmup=2)
+            full = wg2x2.shard.gather_batch(last["y"], total)
+            assert tuple(full.shape) == (total, 1000) and torch.equal(full[lo:hi], last["y"])
+            rec["gather_ms"] = gm
+            rec["gather"] = "NCCL all_gather of the (%d, 1000) logits shards over NVLink, %d ranks" % (n, ctx.world)
         # end to end: images from pinned host memory, logits back to the host
         logits_h = torch.empty((n, 1000)).pin_memory()
         xd = torch.empty_like(imgs[0])
-        e2e_steps = max(3, min(args.steps, 10))
 
-        def e2e():
+        def e2e(i):
             if graphs is not None:      # the captured graph reads imgs[0] and writes outs[0]
                 imgs[0].copy_(imgs_h, non_blocking=True)
                 graphs[0].replay()
@@ -289,37 +525,230 @@ def run_resnet(args, rank, world, local):
                 xd.copy_(imgs_h, non_blocking=True)
                 logits_h.copy_(model(xd), non_blocking=True)
 
-        e2e()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        a.record()
-        for _ in range(e2e_steps):
-            e2e()
-        b.record()
-        torch.cuda.synchronize()
-        te = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms = float(te.item()) / e2e_steps
-    if rank == 0:
-        flops = model.winograd_flops(total)
-        print(json.dumps({
-            "metric": "resnet18_var_forward_throughput", "value": total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
-            "config": {"workload": "cfg4", "total_batch": total, "per_gpu_batch": n, "image": 224,
-                       "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": args.net_layout,
-                       "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; stem, pools, 1x1 shortcuts, BN, FC on stock torch",
-                       "l2": "two rotating image batches; activations of a step exceed L2 many times over",
-                       "launch": "eager" if graphs is None else "one CUDA graph per input buffer"},
-            "winograd_tflops_dense": flops / (ms * 1e-3) / 1e12, "clocks": clocks,
-            "e2e": {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": imgs_h.numel() * 4,
-                    "d2h_bytes_per_step": logits_h.numel() * 4, "ms_per_step": e2e_ms},
-            "gpu_launches": args.steps * 32,
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+        e2e_ms = timed(ctx, e2e, max(3, min(steps, 6)), warmup=1)
+        rec["e2e"] = {"value": total / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": imgs_h.numel() * 4,
+                      "d2h_bytes_per_step": logits_h.numel() * 4, "ms_per_step": e2e_ms}
+    del model, graphs, outs, imgs, last
+    torch.cuda.empty_cache()
+    return rec
+
+
+def reference_gpu(ctx, wl):
+    """The reference's own forward kernels (oracle/_ref/libwg_ref_cuda.so: its *.cu.cc compiled unmodified for sm_100a) on the
+    headline workload: Winograd2x2ImTransComputeLauncher, the ReLU its layer wrapper applies, Winograd2x2ConvComputeLauncher
+    (16 cublasSgemmBatched products in FP32 + Output_transform).  NHWC, forward only, even sizes only (the upstream gradient
+    kernels read out of bounds on odd sizes and are never run here).  A baseline figure, measured beside this library's."""
+    so = os.path.join(ROOT, "oracle", "_ref", "libwg_ref_cuda.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/libwg_ref_cuda.so not built (make -C oracle ref REF=<reference checkout>)"}
+    torch = ctx.torch
+    B, C, K, H, W = wl["B"], wl["C"], wl["K"], wl["H"], wl["W"]
+    if H % 2 or W % 2:
+        return {"unavailable": "odd image size"}
+    ref = ctypes.CDLL(so)
+    Pv = ctypes.c_void_p
+    nH, nW = H // 2, W // 2
+    Xh, Wth = make_inputs(wl, seed=1)
+    xs = [torch.from_numpy(np.ascontiguousarray(np.transpose(Xh, (0, 2, 3, 1)))).to(ctx.dev) + 0.0 * i for i in range(2)]
+    wt = torch.from_numpy(Wth).to(ctx.dev)
+    V = torch.empty((16, B, nH, nW, C), device=ctx.dev)
+    Y = torch.empty((B, H, W, K), device=ctx.dev)
+    tmp = torch.empty(16 * B * nH * nW * K, device=ctx.dev)
+    ptrs = torch.empty(80, dtype=torch.int64, device=ctx.dev)
+    torch.cuda.synchronize()
+
+    def step(i):   # the upstream launchers use the legacy default stream, as does torch here
+        ref.wgref_imtrans(Pv(xs[i % 2].data_ptr()), Pv(V.data_ptr()), C, B, H, W)
+        torch.relu_(V)
+        ref.wgref_conv(Pv(V.data_ptr()), Pv(wt.data_ptr()), Pv(Y.data_ptr()), Pv(tmp.data_ptr()), Pv(ptrs.data_ptr()), C, B, nH, nW, K)
+
+    for i in range(2):
+        step(i)
+    torch.cuda.synchronize()
+    n = 5
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(n):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / n
+    return {"ms_per_step": ms, "img_s": B / (ms * 1e-3), "kind": "_ref", "layout": "NHWC", "dtype": "f32", "steps": n,
+            "what": "upstream imTrans + ReLU + conv launchers (cublasSgemmBatched FP32, cuBLAS handle created and destroyed per call, as upstream)"}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The headline workload
+# ---------------------------------------------------------------------------------------------------------
+def run_layer(args, ctx):
+    import wg2x2  # raises if the CUDA library is missing: there is no fallback
+    torch = ctx.torch
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        wl["B"] = args.batch
+    path = "fused" if args.fused else args.path
+    L = LayerFwd(ctx, wl, args.layout, args.math, path)
+    B, C, K, H, W = wl["B"], wl["C"], wl["K"], wl["H"], wl["W"]
+
+    # ---- the timed region: `steps` launches back to back between two events, nothing else on the stream
+    sampler = ClockSampler(ctx.local)
+    for i in range(args.warmup):
+        L.step(i)
+    ctx.barrier()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.time()
+    t_start.record()
+    for i in range(args.steps):
+        L.step(i)
+    t_end.record()
+    torch.cuda.synchronize()
+    clocks = sampler.finish(wall0, time.time())
+    ctx.barrier()
+    ms_step = ctx.max_over_ranks(t_start.elapsed_time(t_end)) / args.steps
+    check_status(wg2x2)
+
+    pk = peaks()
+    roof, which = L.roofline(pk)
+    traffic = NCU_TRAFFIC.get((args.workload, B, args.layout, which))
+    roof["traffic"], roof["traffic_source"] = (traffic if traffic else (None, None))
+    if L.use_fused and ctx.rank == 0 and not args.only_headline:
+        # for context: the same layer as two kernels with V through HBM, each with its own HBM roofline fraction
+        t1 = timed(Ctx1(ctx), L.imtrans, 50)
+        t2 = timed(Ctx1(ctx), L.conv, 50)
+        k1_bytes, k2_bytes = L.bytesX + L.bytesV, L.bytesV + L.bytesW + L.bytesY
+        roof["two_kernel_path"] = {"imtrans_fwd_ms": t1, "conv_fwd_ms": t2, "imtrans_fwd_frac": k1_bytes / (t1 * 1e-3) / 1e9 / pk["hbm_gbs"],
+                                   "conv_fwd_frac": k2_bytes / (t2 * 1e-3) / 1e9 / pk["hbm_gbs"], "layer_ms": t1 + t2,
+                                   "note": "the same layer as input transform + product kernels with V through HBM (bench.py --path two-kernel)"}
+
+    out = {
+        "metric": METRIC, "value": ctx.world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": ctx.world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
+                   "l2": "%d rotating input buffers (%.0f MB); %.0f MB moved per step" % (L.nbuf, L.nbuf * L.bytesX / 1e6, L.layer_bytes() / 1e6),
+                   "weights": "prepared once outside the timed region (wg2x2_weights_prepare)",
+                   "timing": "two CUDA events around the steps; per-kernel durations from a separate pass afterwards",
+                   "path": "one fused kernel (wg2x2_layer_fwd_prepared's choice for this shape)" if L.use_fused else "two kernels, V through HBM"},
+        "layer_gbs": L.layer_bytes() * ctx.world / (ms_step * 1e-3) / 1e9,
+        "layer_tflops": L.flops * ctx.world / (ms_step * 1e-3) / 1e12,
+        "roofline": roof, "clocks": clocks, "gpu_launches": args.steps * (1 if L.use_fused else 2),
+    }
+
+    # ---- end to end through the public call with host buffers
+    if not args.only_headline:
+        out["e2e"] = run_e2e(args, ctx, L)
+        out["config"]["e2e"] = ("wg2x2.HostLayerPipeline.submit: pinned host X -> pinned host Y every step, %d chunks, H2D / kernels / D2H on "
+                                "three streams, consecutive steps overlapped (two host output buffers)" % args.e2e_chunks)
+    del L
+    torch.cuda.empty_cache()
+
+    # ---- the other workloads, each measured in this run (all ranks take part; cfg4 is sharded over them)
+    if not args.only_headline and not args.no_configs and args.workload == "cfg2" and args.batch == 0:
+        cfgs = {}
+        for name, fn in (("cfg1", lambda: sub_layer_fwd(ctx, "cfg1", args, 200)), ("cfg3", lambda: sub_layer_fwd(ctx, "cfg3", args, 60)),
+                         ("cfg5", lambda: sub_backward(ctx, args, 30)), ("cfg4", lambda: sub_resnet(ctx, args, 8))):
+            try:
+                cfgs[name] = fn()
+            except Exception as e:     # a failed sub-record must not take the headline with it
+                if ctx.world > 1:
+                    raise
+                cfgs[name] = {"error": "%s: %s" % (type(e).__name__, e)}
+        out["configs"] = cfgs
+    if ctx.rank == 0 and not args.only_headline:
+        if args.workload == "cfg2" and args.batch == 0 and not args.no_ref_gpu:
+            try:
+                out["reference_gpu"] = reference_gpu(ctx, wl)
+            except Exception as e:
+                out["reference_gpu"] = {"unavailable": "%s: %s" % (type(e).__name__, e)}
+        if not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(wl)
+            if "configs" in out and "cfg5" in out["configs"] and "error" not in out["configs"]["cfg5"]:
+                out["configs"]["cfg5"]["cpu_baseline"] = cpu_baseline_bwd()
+    if ctx.rank == 0:
+        print(json.dumps(out))
+
+
+class Ctx1:
+    """A view of a Ctx that times on this rank alone (no barrier, no reduction): for context figures taken by rank 0 only."""
+
+    def __init__(self, ctx):
+        self.torch, self.world, self.rank = ctx.torch, 1, ctx.rank
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        return float(ms)
+
+
+def run_e2e(args, ctx, L):
+    """The same layer through wg2x2.HostLayerPipeline.submit: pinned host X -> device -> pinned host Y inside the timed region.
+    Beside it, the two copies alone (no kernels), all ranks at once: the host-side ceiling of the box."""
+    import wg2x2
+    torch = ctx.torch
+    wl = L.wl
+    node = wg2x2.host.bind_to_gpu_node(ctx.local) if not args.no_numa_bind else None   # before the pinned allocations: first touch
+    Xpin = torch.from_numpy(L.Xh).pin_memory()
+    Ypins = [torch.empty(L.Y.shape, dtype=torch.float32).pin_memory() for _ in range(2)]
+    pipe = wg2x2.HostLayerPipeline(wl["B"], wl["H"], wl["W"], wl["C"], wl["K"], layout=L.layout, math=L.math, relu=True, chunks=args.e2e_chunks)
+    e2e_steps = max(3, min(args.steps, 50))
+    done = [None]
+
+    def step(i):   # one host output buffer per step in flight: step n+1 is submitted while step n is still being read back
+        done[0] = pipe.submit(Xpin, L.Wt, Ypins[i % 2])
+
+    for i in range(2):
+        step(i)
+    ctx.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(e2e_steps):
+        step(i)
+    torch.cuda.current_stream().wait_event(done[0])    # the last step's results are in host memory
+    b.record()
+    ctx.barrier()
+    e2e_ms = ctx.max_over_ranks(a.elapsed_time(b)) / e2e_steps
+    # the copies alone, both directions at once on two streams
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    xd, yd = torch.empty_like(L.Xs[0]), L.Y
+    ctx.barrier()
+    n_copy = 5
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    with torch.cuda.stream(s_in):
+        ev[0].record()
+        for _ in range(n_copy):
+            xd.copy_(Xpin, non_blocking=True)
+        ev[1].record()
+    with torch.cuda.stream(s_out):
+        ev[2].record()
+        for _ in range(n_copy):
+            Ypins[0].copy_(yd, non_blocking=True)
+        ev[3].record()
+    ctx.barrier()
+    h2d = n_copy * L.bytesX / (ev[0].elapsed_time(ev[1]) * 1e-3) / 1e9
+    d2h = n_copy * L.bytesY / (ev[2].elapsed_time(ev[3]) * 1e-3) / 1e9
+    return {"value": ctx.world * wl["B"] / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": L.bytesX, "d2h_bytes_per_step": L.bytesY,
+            "ms_per_step": e2e_ms, "h2d_gbs_per_rank": L.bytesX / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": L.bytesY / (e2e_ms * 1e-3) / 1e9,
+            "copies_alone": {"h2d_gbs": -ctx.max_over_ranks(-h2d), "d2h_gbs": -ctx.max_over_ranks(-d2h),
+                             "note": "slowest rank's rate with both directions busy on every rank at once and no kernels: the host-side ceiling"},
+            "host_binding": node}
+
+
+def run_single(args, ctx, rec_fn, metric, scaling, launches_per_step):
+    """--workload cfg4 / cfg5 on their own: the sub-record promoted to a line of its own."""
+    sampler = ClockSampler(ctx.local)
+    wall0 = time.time()
+    rec = rec_fn()
+    clocks = sampler.finish(wall0, time.time())
+    if ctx.rank == 0:
+        out = {"metric": metric, "value": rec["img_s"], "unit": UNIT, "n_gpus": ctx.world, "steps": rec["steps"], "warmup": 3,
+               "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": rec["dtype"],
+               "data": "synthetic", "config": dict({"workload": args.workload}, **{k: v for k, v in rec.items() if k not in ("roofline", "e2e")}),
+               "clocks": clocks, "gpu_launches": rec["steps"] * launches_per_step}
+        for k in ("roofline", "e2e"):
+            if k in rec:
+                out[k] = rec[k]
+        print(json.dumps(out))
 
 
 def main():
@@ -330,7 +759,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--math", default=os.environ.get("WG2X2_BENCH_MATH", "tf32"), choices=["tf32", "fp32"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + ["cfg4", "cfg5"])
-    ap.add_argument("--bwd-math", default="fp32", choices=["fp32", "tf32"], help="cfg5: math mode of the gradient products")
+    ap.add_argument("--bwd-math", default="tf32", choices=["fp32", "tf32"], help="cfg5: math mode of the gradient products")
     ap.add_argument("--stage5-at-14", action="store_true", help="cfg4: leave pool4 out, as the reference script does")
     ap.add_argument("--layout", default="NCHW", choices=["NCHW", "NHWC"])
     ap.add_argument("--batch", type=int, default=0, help="override the per-GPU batch of the workload (profiling on a small case)")
@@ -343,256 +772,29 @@ def main():
                     help="cfg4: physical layout of the activations (NCHW: the 56x56 and 28x28 layers run as one kernel each)")
     ap.add_argument("--no-graph", action="store_true", help="cfg4: launch the network eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="leave out the sub-records of the other workloads")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="leave out the reference's own CUDA kernels")
+    ap.add_argument("--no-numa-bind", action="store_true", help="e2e: do not bind the host thread to the GPU's NUMA node")
+    ap.add_argument("--only-headline", action="store_true",
+                    help="the timed region and the per-kernel pass only (for profiler captures: few launches, small footprint)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "cfg4":
-        if args.impl == "reference":
-            if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "the network-level reference needs TensorFlow 1.3 + tensorpack, "
-                                  "absent here; the layer-level CPU restatement is timed by the cfg2 workload"}))
-            return
-        run_resnet(args, rank, world, local)
-        return
-    if args.workload == "cfg5":
-        if args.impl == "reference":
-            if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "backward CPU timing is not part of the reference arm; "
-                                  "the forward layer (cfg2 workload) is"}))
-            return
-        run_backward(args, rank, world, local)
-        return
-    wl = dict(WORKLOADS[args.workload])
-    if args.batch > 0:
-        wl["B"] = args.batch
-
     if args.impl == "reference":
-        run_reference(args, wl, rank, world)
+        run_reference(args, rank)
         return
-
-    import torch
-    import torch.distributed as dist
-    import wg2x2  # raises if the CUDA library is missing: there is no fallback
-
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    B, C, K, H, W = wl["B"], wl["C"], wl["K"], wl["H"], wl["W"]
-    nH, nW = (H + 1) // 2, (W + 1) // 2
-    P = B * nH * nW
-    Xh, Wth = make_inputs(wl, seed=1 + rank)
-    if args.layout == "NHWC":
-        Xh = np.ascontiguousarray(np.transpose(Xh, (0, 2, 3, 1)))
-    NBUF = 4  # rotating inputs: 4 |X| + the V/Y traffic of a step is well beyond the 126 MB L2
-    Xs = [torch.from_numpy(Xh).to(dev) + 0.0 * i for i in range(NBUF)]
-    Wt = torch.from_numpy(Wth).to(dev)
-    V = torch.empty((16, B, nH, nW, C), device=dev)
-    Y = torch.empty((B, K, H, W) if args.layout == "NCHW" else (B, H, W, K), device=dev)
-    ws_n = wg2x2._lib.lib.wg2x2_conv_fwd_workspace_bytes(B, nH, nW, C, K, wg2x2.ops._MATHS[args.math])
-    ws = torch.empty(max(ws_n, 1), dtype=torch.uint8, device=dev)
-
-    # the weights do not change between forward passes: the tensor-core path repacks them once
-    prepared = wg2x2.prepare_weights(Wt) if args.math == "tf32" else None
-
-    cws_n = wg2x2._lib.lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, nH, nW, C, K) if prepared is not None else 0
-    cws = torch.empty(cws_n, dtype=torch.uint8, device=dev) if cws_n else None   # products of the wide path (C, K >= 256)
-
-    def conv(i):
-        if prepared is not None:
-            wg2x2.conv_fwd_prepared(V, prepared, K, H, W, layout=args.layout, out=Y, workspace=cws)
+    ctx = Ctx()
+    try:
+        if args.workload == "cfg4":
+            run_single(args, ctx, lambda: sub_resnet(ctx, args, max(3, min(args.steps, 30)), total=args.batch or 256),
+                       "resnet18_var_forward_throughput", "strong", 32)
+        elif args.workload == "cfg5":
+            run_single(args, ctx, lambda: sub_backward(ctx, args, max(3, min(args.steps, 200)), math=args.bwd_math, batch=args.batch),
+                       "winograd_relu_conv_layer_bwd_throughput", "weak", 6)
         else:
-            wg2x2.conv_fwd(V, Wt, H, W, layout=args.layout, math=args.math, out=Y, workspace=ws)
-
-    path = "fused" if args.fused else args.path
-    fused_ok = prepared is not None and args.layout == "NCHW" and wg2x2.fused_supported(B, H, W, C, K, "NCHW")
-    fused_pays = K <= 128 or (K <= 256 and C <= 64)          # the library's own rule (wg2x2_layer_fwd_prepared)
-    use_fused = fused_ok and (path == "fused" or (path == "auto" and fused_pays))
-
-    def step(i):
-        if use_fused:
-            wg2x2.layer_fwd_fused(Xs[i % NBUF], prepared, K, relu=True, out=Y)
-            return
-        wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
-        conv(i)
-
-    sampler = ClockSampler(local)
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    # per-kernel events inside the timed region (for the roofline of the dominant kernel)
-    # (on every EV_EVERY-th step: an event record costs about a microsecond of stream time, which is not
-    # negligible next to a 55 us kernel)
-    EV_EVERY = 8 if args.steps >= 64 else 1
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] if i % EV_EVERY == 0 else None for i in range(args.steps)]
-    torch.cuda.synchronize()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
-    wall0 = time.time()
-    t_start.record()
-    for i in range(args.steps):
-        e = ev[i]
-        if e is not None:
-            e[0].record()
-        if use_fused:
-            if e is not None:
-                e[1].record()
-            wg2x2.layer_fwd_fused(Xs[i % NBUF], prepared, K, relu=True, out=Y)
-        else:
-            wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
-            if e is not None:
-                e[1].record()
-            conv(i)
-        if e is not None:
-            e[2].record()
-    t_end.record()
-    torch.cuda.synchronize()
-    wall1 = time.time()
-    clocks = sampler.finish(wall0, wall1)
-    ms_total = t_start.elapsed_time(t_end)
-    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.barrier()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
-    ms_k1 = float(np.mean([e[0].elapsed_time(e[1]) for e in ev if e is not None]))
-    ms_k2 = float(np.mean([e[1].elapsed_time(e[2]) for e in ev if e is not None]))
-    status, where = wg2x2.last_device_status()
-    if status != 0:
-        raise RuntimeError("device status %d at %d" % (status, where))
-
-    # ---- for context next to the one-kernel line: the two-kernel path on the same inputs (short, outside the timed region)
-    two_kernel = None
-    if use_fused and rank == 0:
-        n2 = max(3, min(args.steps, 200))
-        e2 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        for i in range(3):
-            wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V); conv(i)
-        e2[0].record()
-        for i in range(n2):
-            wg2x2.imtrans_fwd(Xs[i % NBUF], relu=True, layout=args.layout, out=V)
-        e2[1].record()
-        for i in range(n2):
-            conv(i)
-        e2[2].record()
-        torch.cuda.synchronize()
-        two_kernel = (e2[0].elapsed_time(e2[1]) / n2, e2[1].elapsed_time(e2[2]) / n2)
-
-    # ---- end to end through the public call with host buffers ------------------------------
-    Xpin = torch.from_numpy(Xh).pin_memory()
-    Ypin = torch.empty(Y.shape, dtype=torch.float32).pin_memory()
-    # the public host-buffer call: chunked, copies and kernels overlapped on three streams
-    pipe = wg2x2.HostLayerPipeline(B, H, W, C, K, layout=args.layout, math=args.math, relu=True, chunks=args.e2e_chunks)
-    e2e_steps = max(3, min(args.steps, 50))
-
-    # one host output buffer per step in flight: step n+1 is submitted while step n is still being read back
-    Ypins = [Ypin, torch.empty(Y.shape, dtype=torch.float32).pin_memory()]
-    e2e_i = [0]
-
-    def e2e_step():
-        e2e_i[0] += 1
-        return pipe.submit(Xpin, Wt, Ypins[e2e_i[0] % 2])
-
-    for _ in range(2):
-        e2e_step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    done = None
-    for _ in range(e2e_steps):
-        done = e2e_step()
-    torch.cuda.current_stream().wait_event(done)    # the last step's results are in host memory
-    b.record()
-    torch.cuda.synchronize()
-    te = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te.item()) / e2e_steps
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    pk = peaks()
-    bytesX, bytesV, bytesY, bytesW = 4 * B * C * H * W, 64 * P * C, 4 * B * K * H * W, 64 * C * K
-    flops = 2.0 * 16 * P * C * K
-    k1_bytes, k2_bytes = bytesX + bytesV, bytesV + bytesW + bytesY
-    tf32_peak = pk["bf16_tflops"] / 2.0
-    k2_t_hbm, k2_t_tensor = k2_bytes / (pk["hbm_gbs"] * 1e9), flops / (tf32_peak * 1e12)
-    if use_fused:
-        fb = bytesX + bytesW + bytesY
-        roof = dict(kernel="layer_fwd_fused (transform + ReLU + products + output transform, one kernel)", bound="hbm",
-                    achieved=fb / (ms_k2 * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"],
-                    note="only X, W and Y cross HBM (%.1f MB); the kernel is paced by the SM, not by HBM: per 128 tiles x 64 channels x "
-                         "64 output channels it issues 288 tcgen05.mma (N=64, K=8; the output transform is folded into 36 signed MMAs per 8 "
-                         "channels instead of 16) and its transform warps compute 16 x 128 x 64 values.  achieved = bytes / the duration of a "
-                         "launch bracketed by events on its own (kernels_ms); back to back the launches overlap their neighbours' tails "
-                         "(programmatic dependent launch), which is why ms_per_step can be below it" % (fb / 1e6),
-                    tensor_tflops_algorithmic=flops / (ms_k2 * 1e-3) / 1e12, tensor_tflops_issued=2.25 * flops / (ms_k2 * 1e-3) / 1e12)
-    elif ms_k2 >= ms_k1:
-        if args.math == "tf32" and k2_t_tensor > k2_t_hbm:
-            roof = dict(kernel="conv_fwd (products + output transform)", bound="tensor", achieved=flops / (ms_k2 * 1e-3) / 1e12,
-                        peak=tf32_peak, unit="TFLOP/s", peak_source=pk["source"] + " bf16 / 2")
-        else:
-            roof = dict(kernel="conv_fwd (products + output transform)", bound="hbm", achieved=k2_bytes / (ms_k2 * 1e-3) / 1e9,
-                        peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"])
-    else:
-        roof = dict(kernel="imtrans_fwd (input transform + ReLU)", bound="hbm", achieved=k1_bytes / (ms_k1 * 1e-3) / 1e9,
-                    peak=pk["hbm_gbs"], unit="GB/s", peak_source=pk["source"])
-    roof["frac"] = roof["achieved"] / roof["peak"]
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the one-pass ncu captures summarised
-    # under profiles/ (taken at this workload's full size); None for shapes that were not captured
-    # (the fused kernel's 60.0 MB = 51.7 MB read + 8.3 MB written inside the launch: most of Y is still dirty in L2 when
-    # the kernel ends and reaches DRAM later; algorithmic X + W + Y = 103 MB)
-    measured_traffic = {("cfg2", 64, "NCHW", "imtrans"): 197.8e6, ("cfg2", 64, "NCHW", "conv"): 224.7e6, ("cfg2", 64, "NCHW", "fused"): 60.0e6}
-    which = "fused" if use_fused else ("conv" if roof["kernel"].startswith("conv") else "imtrans")
-    roof["traffic"] = measured_traffic.get((args.workload, B, args.layout, which))
-    if use_fused:
-        roof["kernels_ms"] = {"layer_fwd_fused": ms_k2}
-        if two_kernel is not None:
-            t1, t2 = two_kernel
-            roof["two_kernel_path"] = {
-                "note": "the same layer as input transform + product kernels with V through HBM (bench.py --path two-kernel), each "
-                        "launched back to back here; their own HBM roofline fractions",
-                "imtrans_fwd_ms": t1, "conv_fwd_ms": t2, "imtrans_fwd_frac": k1_bytes / (t1 * 1e-3) / 1e9 / pk["hbm_gbs"],
-                "conv_fwd_frac": k2_bytes / (t2 * 1e-3) / 1e9 / pk["hbm_gbs"], "layer_ms": t1 + t2}
-    else:
-        roof["kernels_ms"] = {"imtrans_fwd": ms_k1, "conv_fwd": ms_k2}
-        roof["imtrans_fwd_gbs"] = k1_bytes / (ms_k1 * 1e-3) / 1e9
-        roof["conv_fwd_gbs"] = k2_bytes / (ms_k2 * 1e-3) / 1e9
-        roof["conv_fwd_tflops"] = flops / (ms_k2 * 1e-3) / 1e12
-
-    out = {
-        "metric": METRIC, "value": world * B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "tf32" if args.math == "tf32" else "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "layer": wl, "layout": args.layout, "per_gpu_batch": B,
-                   "l2": "4 rotating input buffers; %.0f MB moved per step" % ((bytesX + bytesW + bytesY if use_fused else k1_bytes + k2_bytes) / 1e6),
-                   "weights": "prepared once outside the timed region (wg2x2_weights_prepare)",
-                   "e2e": "wg2x2.HostLayerPipeline.submit: pinned host X -> pinned host Y every step, %d chunks, H2D / kernels / D2H on three "
-                          "streams, consecutive steps overlapped (two host output buffers)" % args.e2e_chunks},
-        "layer_gbs": (bytesX + bytesW + bytesY if use_fused else k1_bytes + k2_bytes) * world / (ms_step * 1e-3) / 1e9,
-        "layer_tflops": flops * world / (ms_step * 1e-3) / 1e12,
-        "roofline": roof, "clocks": clocks,
-        "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": bytesX, "d2h_bytes_per_step": bytesY,
-                "ms_per_step": e2e_ms},
-        "gpu_launches": args.steps * (1 if use_fused else 2),
-    }
-    out["config"]["path"] = "one fused kernel (wg2x2_layer_fwd_prepared's choice for this shape)" if use_fused else "two kernels, V through HBM"
-    if not args.no_cpu_baseline:
-        cb, _, _ = cpu_oracle_rate(wl, args.layout)
-        out["cpu_baseline"] = cb
-    print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+            run_layer(args, ctx)
+    finally:
+        ctx.close()
 
 
 if __name__ == "__main__":

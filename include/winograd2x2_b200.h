@@ -78,7 +78,9 @@ int wg2x2_imtrans_bwd(const float *dV, const float *V_relu, float *dX, int B, in
  * out_h x out_w (2nH-1 <= out_h <= 2nH, same for w).
  * Replaces Winograd2x2ConvComputeLauncher (winograd2x2_conv_op.cc:31,
  * winograd2x2_conv_cuda.cu.cc:65-93): the 16 cublasSgemmBatched products and the
- * Output_transform kernel become one kernel; no product tensor is stored.
+ * Output_transform kernel become one kernel that stores no product tensor -- except for
+ * WG2X2_MATH_TF32 with C, K >= 256 and a workspace that has room for it, where the products
+ * go through scratch memory (see wg2x2_conv_fwd_prepared_ws).
  * workspace: see wg2x2_conv_fwd_workspace_bytes (0 bytes for WG2X2_MATH_FP32).
  */
 int wg2x2_conv_fwd(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K,
@@ -148,7 +150,9 @@ size_t wg2x2_conv_bwd_workspace_bytes(int B, int H, int W, int C, int K, int mat
  *  - Limit: splits * 16*C*K floats <= wg2x2_conv_bwd_dw_noalloc_max_bytes()/4, with the same
  *    split count as wg2x2_conv_bwd; larger problems return WG2X2_ERR_WORKSPACE.
  *  - The first call on each device looks up the array's device address; make that call
- *    before any stream capture.  The call itself allocates nothing.
+ *    before any stream capture.  The call itself allocates nothing.  The address is kept for
+ *    the life of the process: use the device's primary context, and do not call this entry
+ *    point again after cudaDeviceReset (the kept address would be stale).
  *  - Every call shares the one array: calls that overlap on the GPU (two streams, two
  *    threads) race.  Nothing in it needs clearing: each call overwrites all it later reads.
  * Arguments as in wg2x2_conv_bwd; the result equals its dW bit for bit.
@@ -203,6 +207,25 @@ int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y,
  * Synchronises the given stream.
  */
 int wg2x2_last_device_status(void *stream, unsigned int *where);
+
+/*
+ * Bounded waits.  Every device-side wait of the tensor-core kernels (on an mbarrier fed by a TMA copy, by
+ * tcgen05.commit or by another warp) polls at most `polls` times; when one runs out, the role records where it
+ * was, raises a CTA-wide flag that makes the other roles leave, the kernel frees its tensor memory and returns,
+ * and wg2x2_last_device_status reports WG2X2_ERR_TIMEOUT once (reading clears it).  The outputs of such a launch
+ * are incomplete: a caller that cannot afford that polls the status after its last launch.  polls = 0 restores
+ * the default (4e7, about a second).  Process-wide; read by each launch when it is enqueued.
+ * The reference has no counterpart: its kernels never wait on one another.
+ */
+int wg2x2_set_wait_limit(long long polls);
+/*
+ * Test hooks for the time-out path (they fault and hang nothing).  wg2x2_test_drop_load(n): in the next
+ * launch of conv_fwd (row-walk) or layer_fwd_fused, CTA 0's weight producer stops before its n-th load, so the
+ * MMA issuer's wait for that stage runs out; one-shot, n < 0 disarms.  wg2x2_test_wait_probe: a one-thread
+ * kernel that waits `polls` polls on a barrier nobody arrives on and records `where`.
+ */
+int wg2x2_test_drop_load(int nth);
+int wg2x2_test_wait_probe(long long polls, unsigned int where, void *stream);
 
 #ifdef __cplusplus
 }

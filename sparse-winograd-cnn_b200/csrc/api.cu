@@ -21,6 +21,9 @@ size_t conv_fwd_tc_workspace_bytes(int B, int nH, int nW, int C, int K);
 int conv_fwd_tc(const float *V, const float *Wt, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW, int layout,
                 void *ws, size_t ws_bytes, cudaStream_t st);
 int tc_last_device_status(cudaStream_t st, unsigned int *where);
+int tc_set_wait_limit(long long polls);
+int tc_test_drop_load(int nth);
+int tc_wait_probe(long long polls, unsigned where, cudaStream_t st);
 size_t prepared_weights_bytes(int C, int K);
 int weights_prepare(const float *Wt, int C, int K, void *prepared, size_t bytes, cudaStream_t st);
 int conv_fwd_tc_prepared(const float *V, const void *prepared, float *Y, int B, int nH, int nW, int C, int K, int outH, int outW,
@@ -246,6 +249,15 @@ int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y,
 int wg2x2_last_device_status(void *stream, unsigned int *where)
 {
     return tc_last_device_status((cudaStream_t)stream, where);
+}
+
+int wg2x2_set_wait_limit(long long polls) { return tc_set_wait_limit(polls); }
+
+int wg2x2_test_drop_load(int nth) { return tc_test_drop_load(nth); }
+
+int wg2x2_test_wait_probe(long long polls, unsigned int where, void *stream)
+{
+    return tc_wait_probe(polls, where, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -16,6 +16,7 @@
 // and returns (status readable through wg2x2_last_device_status).
 #include <cuda.h>
 
+#include <atomic>
 
 #include "wg_common.cuh"
 
@@ -35,7 +36,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kCtrlBytes = 1024;                   // barriers, TMEM pointer, abort flag, per-role block masks
 constexpr int kEpiStageBytes = 32 * 32 * 4;        // per epilogue warp: 32 tiles x 32 channels, for coalesced NHWC stores
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + kCtrlBytes + kEpiWarps * kEpiStageBytes;
-constexpr long long kSpinLimit = 40LL * 1000 * 1000;  // try_wait polls before a wait gives up (~ a second)
+constexpr uint32_t kSpinLimit = 40u * 1000 * 1000;   // try_wait polls before a wait gives up (~ a second)
 
 __device__ unsigned int g_tc_status[2];  // [0] = 0 ok / 1 timeout, [1] = where (role<<8 | detail)
 __device__ unsigned int g_tc_diag[32];   // after a timeout: per role (where >> 8), the wait it was in when it gave up or was told to
@@ -75,9 +76,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up (or when another role already did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where,
+                                          uint32_t limit = kSpinLimit)
 {
-    for (long long it = 0; it < kSpinLimit; ++it) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 1023) == 1023 && *abort_flag) { g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x40000000u; return false; }
     }
@@ -92,9 +94,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // iterations, and what follows (tcgen05.ld / tcgen05.st / tcgen05.wait) is .sync.aligned, which a diverged
 // warp must not execute.  The vote brings the lanes back together and makes the outcome (and so every
 // break out of the role's loop) the same for all of them.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where)
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where,
+                                               uint32_t limit = kSpinLimit)
 {
-    const bool ok = mbar_wait(bar, parity, abort_flag, where);
+    const bool ok = mbar_wait(bar, parity, abort_flag, where, limit);
     return __all_sync(0xffffffffu, ok);
 }
 
@@ -227,6 +230,8 @@ struct TcParams {
     int nMT, nKB, nCC;   // m-tiles, 64-channel blocks, 32-channel chunks
     int tpu;             // tiles per unit (<= 128): chosen so that the units divide evenly over the SMs
     int units;
+    uint32_t spin_limit;    // polls before a wait gives up (wg2x2_set_wait_limit)
+    int drop_load;          // >= 0: the producer of CTA 0 leaves out its drop_load-th stage (wg2x2_test_drop_load), else -1
 };
 
 // EXTRAS: compile the optional epilogue affine map and residual addition in (kept out of the plain kernel,
@@ -280,6 +285,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             int s = 0; uint32_t ph = 0;
             bool ok = true;
             int tr = 0; (void)tr;
+            int nload = 0;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 const int mt = u / prm.nKB, kb = u % prm.nKB;
                 const int p0 = mt * prm.tpu, k0 = kb * kBlockN;
@@ -288,8 +294,10 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                     const unsigned long long mk = role_masks[t];
                     for (int cc = 0; cc < nCC; ++cc) {
                         if (cc > 0 && cc < 64 && !((mk >> cc) & 1ull)) continue;   // all-zero weight block: nothing to add
-                        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x100u | s)) { ok = false; break; }
+                        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x100u | s, prm.spin_limit)) { ok = false; break; }
                         TC_TRACE(tr); ++tr;
+                        // test hook: this stage is never filled (nothing is put in flight), so the issuer's wait on it runs out
+                        if (blockIdx.x == 0 && nload++ == prm.drop_load) { ok = false; break; }
                         mbar_expect_tx(full_bar(s), kStageBytes);
                         const uint32_t a_dst = base + s * kStageBytes;
                         tma_load_3d(a_dst, &mapA, full_bar(s), cc * kBlockK, p0, t);
@@ -318,7 +326,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                 for (int i = 0; i < 4 && ok; ++i) {
                     const int buf = i & 1;
                     // the epilogue must have drained this accumulator buffer
-                    if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf)) { ok = false; break; }
+                    if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf, prm.spin_limit)) { ok = false; break; }
                     acc_use[buf]++;
                     tc_fence_after();
                     for (int j = 0; j < 4 && ok; ++j) {
@@ -327,7 +335,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 4 * kBlockN + j * kBlockN);
                         for (int cc = 0; cc < nCC; ++cc) {
                             if (cc > 0 && cc < 64 && !((mk >> cc) & 1ull)) continue;
-                            if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s)) { ok = false; break; }
+                            if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s, prm.spin_limit)) { ok = false; break; }
                             TC_TRACE(512 + tr);
                             tc_fence_after();
                             const uint32_t a_addr = base + s * kStageBytes;
@@ -365,7 +373,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int buf = i & 1;
-                if (ok && !mbar_wait_warp(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf)) ok = false;
+                if (ok && !mbar_wait_warp(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x400u | (ew << 4) | buf, prm.spin_limit)) ok = false;
                 acc_use[buf]++;
                 if (ok) {
                     if (ew == 0 && lane == 0) TC_TRACE(1536 + 4 * tr);
@@ -520,6 +528,43 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
+// Poll limit of the bounded waits and the one-shot test hook, handed to every launch through its parameters.
+static std::atomic<uint32_t> g_wait_limit{kSpinLimit};
+static std::atomic<int> g_drop_load{-1};
+
+int tc_set_wait_limit(long long polls)
+{
+    if (polls < 0 || polls > 0xFFFFFFFFLL) return WG2X2_ERR_BAD_ARG;
+    g_wait_limit.store(polls == 0 ? kSpinLimit : (uint32_t)polls);
+    return WG2X2_OK;
+}
+int tc_test_drop_load(int nth)
+{
+    g_drop_load.store(nth < 0 ? -1 : nth);
+    return WG2X2_OK;
+}
+static uint32_t wait_limit() { return g_wait_limit.load(); }
+static int take_drop_load() { return g_drop_load.exchange(-1); }   // consumed by the next launch that looks at it
+
+// Smallest possible exercise of the bounded wait: one thread waits on a barrier nobody arrives on.
+__global__ void wait_probe_kernel(uint32_t limit, unsigned where)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_wait(smem_u32(&bar), 0, &abort_flag, where, limit);
+    }
+}
+int tc_wait_probe(long long polls, unsigned where, cudaStream_t st)
+{
+    if (polls <= 0 || polls > (long long)kSpinLimit) return WG2X2_ERR_BAD_ARG;
+    wait_probe_kernel<<<1, 32, 0, st>>>((uint32_t)polls, where);
+    return launch_status();
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -610,6 +655,8 @@ static int tc_launch(int layout, const float *A, const float *Bop, const unsigne
     }
     prm.nMT = (int)cdivll(P, prm.tpu);
     prm.units = prm.nMT * prm.nKB;
+    prm.spin_limit = wait_limit();
+    prm.drop_load = take_drop_load();
     CUtensorMap mapA, mapB;
     if (!make_map(&mapA, A, contr, P, kBlockM)) return WG2X2_ERR_LAUNCH;
     if (!make_map(&mapB, Bop, contr, ncols, kBlockN)) return WG2X2_ERR_LAUNCH;

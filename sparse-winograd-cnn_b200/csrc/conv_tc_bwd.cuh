@@ -7,6 +7,8 @@
 //   dW_t = V_t^T . dM_t      conv_grad_gemm_tc_kernel<0> (both operands MN-major), split over P
 #pragma once
 
+static inline bool misaligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }   // NULL passes
+
 // ---------------------------------------------------------------------------------------
 // dM producer
 // ---------------------------------------------------------------------------------------
@@ -156,10 +158,25 @@ __global__ void __launch_bounds__(256, 3) conv_dm_nchw_vec_kernel(const float *_
     }
 }
 
-__global__ void __launch_bounds__(256) round_tf32_kernel(const float *__restrict__ src, float *__restrict__ dst, long long n)
+// W (16, C, K) -> W rounded to TF32, plus the zero-block map of the forward's prepared weights: bit cc of
+// map[t][kb] is set when the block (input channels cc*32.., output channels kb*64..) holds a non-zero.
+// One CTA per block: 32 rows of 64 consecutive floats.
+__global__ void __launch_bounds__(256) round_and_map_kernel(const float *__restrict__ Wt, float *__restrict__ Wr,
+                                                              unsigned long long *__restrict__ map, int C, int K, int nKB, int nCC)
 {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-        dst[i] = round_tf32(__ldg(src + i));
+    const int kb = blockIdx.x, cc = blockIdx.y, t = blockIdx.z;
+    int nz = 0;
+    for (int e = threadIdx.x; e < 32 * 64; e += 256) {
+        const int c = cc * 32 + (e >> 6), k = kb * 64 + (e & 63);
+        if (c < C && k < K) {
+            const long long o = ((long long)t * C + c) * K + k;
+            const float w = round_tf32(__ldg(Wt + o));
+            Wr[o] = w;
+            nz |= (w != 0.f);
+        }
+    }
+    nz = __syncthreads_or(nz);
+    if (threadIdx.x == 0 && nz && nCC <= 64) atomicOr(map + (long long)t * nKB + kb, 1ull << cc);
 }
 
 static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int layout, cudaStream_t st)
@@ -200,7 +217,7 @@ static int launch_dm(const float *dY, float *dM, int B, int H, int W, int K, int
 // Workspace of the tensor-core backward pass: [dM | W rounded to TF32 | dW partials]
 // ---------------------------------------------------------------------------------------
 struct BwdWs {
-    size_t dm, wr, partial, total;
+    size_t dm, wr, map, partial, total;
 };
 static BwdWs bwd_ws_layout(long long P, int C, int K, int dw_splits)
 {
@@ -208,6 +225,7 @@ static BwdWs bwd_ws_layout(long long P, int C, int K, int dw_splits)
     w.dm = 0;
     size_t off = align_up((size_t)16 * P * K * sizeof(float), 256);
     w.wr = off;      off += align_up((size_t)16 * C * K * sizeof(float), 256);
+    w.map = off;     off += align_up((size_t)16 * cdiv(K, 64) * sizeof(unsigned long long), 256);
     w.partial = off; off += dw_splits > 1 ? align_up((size_t)dw_splits * 16 * C * K * sizeof(float), 256) : 0;
     w.total = off;
     return w;
@@ -254,7 +272,36 @@ struct GgParams {
     int splits, chunks_per_split;
     int units;
     int direct;
+    // Zero-block skipping (KIND 1 only).  block_map[t][kb] has bit cc set when the 64 x 32 weight block (output
+    // channels kb*64.., input channels cc*32..) of position t holds a non-zero (pack_weights_kernel / block_map_kernel).
+    //   map_mode 1: columns = output channels, contraction over input channels (forward products)
+    //   map_mode 2: columns = input channels, contraction over output channels (dV)
+    //   map_mode 0: every chunk runs
+    const unsigned long long *block_map;
+    int map_mode, map_nkb;
 };
+
+// Bit n of the result is set when contraction chunk n (32 elements) of this unit has to run: the first chunk always
+// (it zero-initialises the accumulator), a later one unless every weight block it would multiply is all zero.
+// Contractions of more than 64 chunks run in full.
+__device__ __forceinline__ unsigned long long gg_live_chunks(const GgParams &prm, int t, int cb)
+{
+    if (prm.map_mode == 0 || prm.contr > 64 * 32) return ~0ull;
+    const unsigned long long *row = prm.block_map + (long long)t * prm.map_nkb;
+    unsigned long long live = 1ull;
+    if (prm.map_mode == 1) {
+        const int kb0 = cb * (prm.N >> 6), kb1 = min(prm.map_nkb, kb0 + max(prm.N >> 6, 1));
+        for (int kb = kb0; kb < kb1; ++kb) live |= __ldg(row + kb);
+    } else {
+        const int c0 = cb * (prm.N >> 5), nc = prm.N >> 5;                 // 32-channel chunks covered by this unit's columns
+        if (c0 + nc > 64) return ~0ull;
+        const unsigned long long sel = (nc >= 64 ? ~0ull : ((1ull << nc) - 1ull)) << c0;
+        const int nkb = (int)((prm.contr + 63) >> 6);
+        for (int kb = 0; kb < nkb && kb < prm.map_nkb; ++kb)
+            if (__ldg(row + kb) & sel) live |= 3ull << (2 * kb);          // both 32-wide halves of the 64-wide block
+    }
+    return live;
+}
 
 // MN-major TF32 operand.  The only shared-memory layout UMMA accepts for it is the 128-byte swizzle with a
 // 32-byte base (layout type 1; TMA writes it with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B): rows of 128 bytes,
@@ -324,7 +371,9 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                 decode(u, split, t, rb, cb);
                 const long long kbeg = (long long)split * prm.chunks_per_split * 32;
                 const long long kend = min(prm.contr, kbeg + (long long)prm.chunks_per_split * 32);
+                const unsigned long long live = KIND == 1 ? gg_live_chunks(prm, t, cb) : ~0ull;
                 for (long long kc = kbeg; kc < kend; kc += 32) {
+                    if (KIND == 1 && kc < 64 * 32 && !((live >> (kc >> 5)) & 1ull)) continue;   // all-zero weight blocks: nothing to add
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x500u | s)) { ok = false; break; }
                     mbar_expect_tx(full_bar(s), stage_tx);
                     const uint32_t a_dst = base + s * kGgStageBytes;
@@ -362,7 +411,9 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 256);
                 uint32_t first = 1;
+                const unsigned long long live = KIND == 1 ? gg_live_chunks(prm, t, cb) : ~0ull;
                 for (long long kc = kbeg; kc < kend; kc += 32) {
+                    if (KIND == 1 && kc < 64 * 32 && !((live >> (kc >> 5)) & 1ull)) continue;
                     if (!mbar_wait(full_bar(s), ph, abort_flag, 0x700u | s)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = base + s * kGgStageBytes;
@@ -525,6 +576,7 @@ int conv_dw_tc(const float *V, const float *dM, const float *mask, float *dW, fl
     prm.direct = prm.splits == 1;
     prm.out = prm.direct ? dW : partial;
     prm.mask = mask;
+    prm.block_map = nullptr; prm.map_mode = 0; prm.map_nkb = 0;
     CUtensorMap mapV, mapM;
     if (!make_map_gg(&mapV, V, C, P, true, 32) || !make_map_gg(&mapM, dM, K, P, true, 32)) return WG2X2_ERR_LAUNCH;
     const int s = gg_launch<0>(mapV, mapM, prm, st);
@@ -533,12 +585,14 @@ int conv_dw_tc(const float *V, const float *dM, const float *mask, float *dW, fl
     return launch_status();
 }
 
-int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, float *dV, long long P, int C, int K, int relu,
-               cudaStream_t st)
+int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, unsigned long long *map, float *dV, long long P, int C,
+               int K, int relu, cudaStream_t st)
 {
     if (P > 0x7fffffffLL - 128) return WG2X2_ERR_UNSUPPORTED;
-    const long long n = (long long)16 * C * K;
-    round_tf32_kernel<<<(int)min((long long)kNumSMs * 8, cdivll(n, 256)), 256, 0, st>>>(Wt, Wr, n);
+    const int nKB = cdiv(K, 64), nCC = cdiv(C, 32);
+    if (nCC > 65535) return WG2X2_ERR_UNSUPPORTED;
+    if (cudaMemsetAsync(map, nCC <= 64 ? 0 : 0xFF, (size_t)16 * nKB * sizeof(unsigned long long), st) != cudaSuccess) return WG2X2_ERR_LAUNCH;
+    round_and_map_kernel<<<dim3(nKB, nCC, 16), 256, 0, st>>>(Wt, Wr, map, C, K, nKB, nCC);
     if (launch_status() != WG2X2_OK) return WG2X2_ERR_LAUNCH;
     GgParams prm;
     prm.rows = P; prm.cols = C; prm.contr = K;
@@ -551,6 +605,7 @@ int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, floa
     prm.direct = 1;
     prm.out = dV;
     prm.mask = relu ? V : nullptr;
+    prm.block_map = map; prm.map_mode = 2; prm.map_nkb = nKB;
     CUtensorMap mapA, mapB;
     if (!make_map_gg(&mapA, dM, K, P, false, 128) || !make_map_gg(&mapB, Wr, K, C, false, prm.N)) return WG2X2_ERR_LAUNCH;
     return gg_launch<1>(mapA, mapB, prm, st);
@@ -566,6 +621,10 @@ int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *m
                 int C, int K, int layout, int relu, void *ws, size_t ws_bytes, cudaStream_t st)
 {
     if (!tc_bwd_shape_supported(C, K)) return WG2X2_ERR_UNSUPPORTED;
+    // TMA bases and the 16-byte loads/stores of the producer and the epilogues: every operand that is given
+    // must sit on a 16-byte boundary (checked before anything is enqueued)
+    if (misaligned16(V) || misaligned16(Wt) || misaligned16(dY) || misaligned16(mask) || misaligned16(dV) || misaligned16(dW))
+        return WG2X2_ERR_BAD_ARG;
     const int nH = (H + 1) / 2, nW = (W + 1) / 2;
     const long long P = (long long)B * nH * nW;
     const int splits = dW ? conv_dw_tc_splits(P, C, K) : 1;
@@ -576,7 +635,8 @@ int conv_bwd_tc(const float *V, const float *Wt, const float *dY, const float *m
     int s = launch_dm(dY, dM, B, H, W, K, layout, st);
     if (s != WG2X2_OK) return s;
     if (dV) {
-        s = conv_dv_tc(V, Wt, dM, reinterpret_cast<float *>(wsb + lay.wr), dV, P, C, K, relu, st);
+        s = conv_dv_tc(V, Wt, dM, reinterpret_cast<float *>(wsb + lay.wr), reinterpret_cast<unsigned long long *>(wsb + lay.map), dV,
+                       P, C, K, relu, st);
         if (s != WG2X2_OK) return s;
     }
     if (dW) {
@@ -697,6 +757,10 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
 {
     const long long P = (long long)B * nH * nW;
     if (P > 0x7fffffffLL - 128) return WG2X2_ERR_UNSUPPORTED;
+    if (!V || !prepared || !Y) return WG2X2_ERR_BAD_ARG;
+    if (misaligned16(V) || misaligned16(prepared) || misaligned16(Y) || misaligned16(out_scale) || misaligned16(out_shift) ||
+        misaligned16(residual))
+        return WG2X2_ERR_BAD_ARG;
     if (!ws || ws_bytes < conv_fwd_wide_workspace_bytes(P, K) || (reinterpret_cast<uintptr_t>(ws) & 255u)) return WG2X2_ERR_WORKSPACE;
     float *M = static_cast<float *>(ws);
     GgParams prm;
@@ -710,6 +774,10 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
     prm.direct = 1;
     prm.out = M;
     prm.mask = nullptr;
+    // the zero-block map that weights_prepare built behind the packed weights
+    prm.block_map = reinterpret_cast<const unsigned long long *>(static_cast<const unsigned char *>(prepared) +
+                                                                 align_up((size_t)16 * K * C * sizeof(float), 256));
+    prm.map_mode = 1; prm.map_nkb = cdiv(K, kBlockN);
     CUtensorMap mapA, mapB;
     if (!make_map_gg(&mapA, V, C, P, false, 128) || !make_map_gg(&mapB, static_cast<const float *>(prepared), C, K, false, prm.N))
         return WG2X2_ERR_LAUNCH;

@@ -72,12 +72,15 @@ struct FuParams {
     const float *out_scale, *out_shift;
     int accumulate;                        // Y already holds the shortcut: add to it (TMA reduce) instead of overwriting
     const float *in_scale, *in_shift;      // per input channel, applied to the image before the transform (AFFINE)
+    const unsigned long long *masks;       // zero-block map of the prepared weights: bit cc of masks[t][kb]
     int B, H, W, C, K, nH, nW, outH, outW;
     int TH, TW, NB, BW, BWY;         // block of tiles; BW = width of the input box, BWY = of the output box
     int lp_log2;                     // a tile row takes 2^lp_log2 >= TW TMEM lanes
     int nRB, nSeg, nGroups, nKB, nC32;        // nC32 = ring slots (32 input channels each) per Winograd row
     int units, relu;
     uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows) and of the row-stride-2 (TH+1 rows) box
+    uint32_t spin_limit;             // polls before a wait gives up (wg2x2_set_wait_limit)
+    int drop_load;                   // >= 0: the W producer of CTA 0 leaves out its drop_load-th slot (wg2x2_test_drop_load), else -1
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
@@ -89,9 +92,10 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
 
 // Bounded wait for roles that can afford a late wake-up: sleeps between polls, so that the waiting warp leaves
 // the issue slots of its scheduler to the warps that have work.
-__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where, unsigned ns)
+__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned where, unsigned ns,
+                                                 uint32_t limit = kSpinLimit)
 {
-    for (long long it = 0; it < kSpinLimit / 8; ++it) {
+    for (uint32_t it = 0; it < limit / 8 + 1; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(ns);
         if ((it & 255) == 255 && *abort_flag) { g_tc_diag[(where >> 8) & 31] = where | (parity << 16) | 0x40000000u; return false; }
@@ -197,7 +201,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
     constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
                   kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXfull, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
-    static_assert((kB8 + 2) * 8 <= kCtrlBytes, "control block");
+    static_assert((kB8 + 2) <= 32 && (32 + 4 * 16) * 8 <= kCtrlBytes, "control block: barriers, then the issuers' zero-block words");
     auto full_bar = [&](int g) { return bars + 8u * (kB0 + g); };
     auto free_bar = [&](int g) { return bars + 8u * (kB1 + g); };
     auto accf_bar = [&](int b) { return bars + 8u * (kB4 + b); };
@@ -266,12 +270,21 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             int i = 0, cc = 0;
             uint32_t units_done = 0;
             int trm = 0; (void)trm;
+            // this issuer's copy of the unit's sixteen zero-block words (bit cc: the [64 x 32] weight tile of position t,
+            // input channels cc*32.., holds a non-zero)
+            unsigned long long *my_masks = reinterpret_cast<unsigned long long *>(bars_gen + 32 + warp * 16);
+            const uint32_t *my_masks32 = reinterpret_cast<const uint32_t *>(my_masks);
             for (int n = 0; n < total; ++n) {
+                if (cc == 0 && i == 0) {
+                    int gu, rbu, segu, kbu;
+                    decode((int)blockIdx.x + (int)units_done * (int)gridDim.x, gu, rbu, segu, kbu);
+                    load_unit_masks(prm.masks, prm.nKB, kbu, my_masks);
+                }
                 if (warp == 0) TC_TRACE(1024 + 5 * trm);
-                if (!mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g)) break;
+                if (!mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g, prm.spin_limit)) break;
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 1);
                 // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
-                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a)) break;
+                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a, prm.spin_limit)) break;
                 if (warp == 0) TC_TRACE(1024 + 5 * trm + 2);
                 tc_fence_after();
                 int g2 = g + 1; uint32_t gph2 = gph;
@@ -281,6 +294,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
 #pragma unroll
                     for (int jj = 0; jj < 3; ++jj) {
+                        // an all-zero weight tile adds nothing (the slot's first chunk always runs: it zero-initialises)
+                        if (cc > 0 && cc < 64 && !((my_masks32[2 * (4 * i + e + jj) + (cc >> 5)] >> (cc & 31)) & 1u)) continue;
                         const bool neg_e = (e == 1 && jj >= 1);                      // At[1][j] = -1 for j = 2, 3
                         const uint32_t idesc = (neg_a != neg_e) ? idesc_neg : idesc_pos;
                         const uint32_t aj = a_tmem + (uint32_t)(jj * 32), bj = b_lo + (uint32_t)(jj * (kFuWTile >> 4));
@@ -311,7 +326,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     const CUtensorMap *map = strided ? &mapX2 : &mapX1;
                     const uint32_t bytes = strided ? prm.xbytes2 : prm.xbytes1;
                     for (int cc = 0; cc < 2 * nC32; ++cc) {     // channels beyond C arrive as zeros
-                        if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100)) { ok = false; break; }
+                        if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100, prm.spin_limit)) { ok = false; break; }
                         TC_TRACE(trx); ++trx;
                         mbar_expect_tx(xfull_bar(xj), bytes);
                         tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xj), x0, h_lo, cc * 16, b0);
@@ -326,12 +341,15 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             // ------------------------------ W producer -----------------------------------
             int s = 0; uint32_t ph = 0;
             bool ok = true;
+            int nload = 0;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 int g, rb, seg, kb;
                 decode(u, g, rb, seg, kb);
                 for (int i = 0; i < 4 && ok; ++i)
                     for (int cc = 0; cc < nC32; ++cc) {
-                        if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100)) { ok = false; break; }
+                        if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100, prm.spin_limit)) { ok = false; break; }
+                        // test hook: this slot's weights never arrive (nothing is put in flight), so the issuers' wait on it runs out
+                        if (blockIdx.x == 0 && nload++ == prm.drop_load) { ok = false; break; }
                         mbar_expect_tx(full_bar(s), kFuWBytes);
                         tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), cc * 32, kb * kBlockN, 4 * i);
                         if (++s == kFuWStages) { s = 0; ph ^= 1u; }
@@ -421,9 +439,9 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             // both waits, then one vote (the warp converged and of one mind before the aligned instructions below)
-            const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj);
+            const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, prm.spin_limit);
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            const bool got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g);
+            const bool got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, prm.spin_limit);
             if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
@@ -520,7 +538,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
                 if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a);
-                if (!__all_sync(0xffffffffu, mbar_wait_sleepy(accf_bar(a), units_done & 1u, abort_flag, 0x400u | (ew << 4) | a, 400))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_sleepy(accf_bar(a), units_done & 1u, abort_flag, 0x400u | (ew << 4) | a, 400, prm.spin_limit))) { ok = false; break; }
                 if (ew == 0 && lane == 0) TC_TRACE(2048 + 4 * (int)units_done + 2 * a + 1);
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * 2 * kBlockN + half * 32);
@@ -542,7 +560,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                         mbar_arrive(yfree_bar(half));
                     }
-                    if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew)) { ok = false; break; }
+                    if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew, prm.spin_limit)) { ok = false; break; }
                     float *stage = stage0;
                     if (live) {
 #pragma unroll
@@ -563,7 +581,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     if (lane == 0) mbar_arrive(ywritten_bar(half));
                     bool stored = true;
                     if (elected) {
-                        stored = mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew);
+                        stored = mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew, prm.spin_limit);
                         if (stored && kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
                             if (prm.accumulate) tma_reduce_add_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
                             else tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
@@ -660,8 +678,12 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
         cudaMemcpyAsync(Y, residual, sizeof(float) * (size_t)B * K * H * W, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
         return WG2X2_ERR_LAUNCH;
     p.in_scale = in_scale; p.in_shift = in_shift;
+    p.masks = reinterpret_cast<const unsigned long long *>(static_cast<const unsigned char *>(prepared) +
+                                                           align_up((size_t)16 * K * C * sizeof(float), 256));
     p.B = B; p.H = H; p.W = W; p.C = C; p.K = K; p.outH = H; p.outW = W; p.relu = relu;
     if (!fused_geometry(p)) return WG2X2_ERR_UNSUPPORTED;
+    p.spin_limit = wait_limit();
+    p.drop_load = take_drop_load();
     EncodeTiledFn fn = encode_fn();
     if (!fn) return WG2X2_ERR_LAUNCH;
     CUtensorMap mapX1, mapX2, mapW, mapY;

@@ -1,9 +1,52 @@
 """Layer forward for batches that live in host memory: the batch is cut into chunks and the
 host-to-device copy of chunk i+1, the kernels of chunk i and the device-to-host copy of chunk i-1
 run on three CUDA streams, so that the PCIe link is busy in both directions while the GPU works."""
+import os
+
 import torch
 
 from . import ops
+
+
+def _parse_cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_host_node(index, sysfs="/sys/bus/pci/devices"):
+    """(NUMA node, set of CPUs) next to GPU `index` as sysfs reports them for its PCI function, or (None, None)
+    when that cannot be read (no sysfs entry, a virtual machine that hides the topology)."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        base = os.path.join(sysfs, bdf)
+        node = int(open(os.path.join(base, "numa_node")).read())
+        cpus = _parse_cpulist(open(os.path.join(base, "local_cpulist")).read())
+        return (node if node >= 0 else None), (cpus or None)
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None, None
+
+
+def bind_to_gpu_node(index):
+    """Restrict this process to the CPUs next to GPU `index`, so that the pinned host buffers it allocates afterwards
+    (first touch) and the thread that feeds the copies sit on the GPU's NUMA node / PCIe root.  Call it before allocating
+    pinned memory.  Returns what was done, for the record; binds nothing when the topology cannot be read or when the
+    GPU's CPUs are all this process may use anyway."""
+    node, cpus = gpu_host_node(index)
+    allowed = os.sched_getaffinity(0)
+    if not cpus:
+        return {"numa_node": node, "bound": False, "why": "topology not readable", "cpus_allowed": len(allowed)}
+    want = cpus & allowed
+    if not want or want == allowed:
+        return {"numa_node": node, "bound": False, "why": "the GPU's CPUs are all of this process's CPUs" if want else "no overlap",
+                "cpus_allowed": len(allowed)}
+    os.sched_setaffinity(0, want)
+    return {"numa_node": node, "bound": True, "cpus": len(want), "cpus_allowed": len(allowed)}
 
 
 class HostLayerPipeline:

@@ -15,6 +15,29 @@ def _chk(t, name):
     return t
 
 
+def _chk_shape(t, shape, name):
+    """Optional tensor `t` must be a contiguous float32 CUDA tensor of exactly `shape`."""
+    if t is None:
+        return None
+    _chk(t, name)
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError("%s has shape %s, expected %s" % (name, tuple(t.shape), tuple(shape)))
+    return t
+
+
+def _chk_prepared(prepared, C, K):
+    """`prepared` comes from prepare_weights for exactly this (C, K): the kernels build their TMA maps over it
+    from C and K alone, so a buffer made for other sizes would be read past its end."""
+    if not (isinstance(prepared, torch.Tensor) and prepared.is_cuda and prepared.dtype == torch.uint8):
+        raise TypeError("prepared must be the buffer returned by prepare_weights")
+    ck = getattr(prepared, "_wg_ck", None)
+    if ck is not None and ck != (C, K):
+        raise ValueError("prepared weights are for (C, K) = %s, the call has %s" % (ck, (C, K)))
+    if prepared.numel() < lib.wg2x2_prepared_weights_bytes(C, K):
+        raise ValueError("prepared weight buffer too small for C=%d K=%d" % (C, K))
+    return prepared
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -108,13 +131,14 @@ def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out
     layout = _LAYOUTS[layout]
     _chk(V, "V")
     _, B, nH, nW, C = V.shape
+    _chk_prepared(prepared, C, K)
     out_h = 2 * nH if out_h is None else out_h
     out_w = 2 * nW if out_w is None else out_w
-    Y = out if out is not None else torch.empty(_img_shape(B, out_h, out_w, K, layout), dtype=torch.float32, device=V.device)
+    yshape = _img_shape(B, out_h, out_w, K, layout)
+    Y = _chk_shape(out, yshape, "out") if out is not None else torch.empty(yshape, dtype=torch.float32, device=V.device)
+    _chk_shape(out_scale, (K,), "out_scale"); _chk_shape(out_shift, (K,), "out_shift"); _chk_shape(residual, yshape, "residual")
     nws = lib.wg2x2_conv_fwd_prepared_workspace_bytes(B, nH, nW, C, K) if wide else 0
     if nws:   # many channels: products as wide GEMMs into scratch memory, then the output transform
-        if residual is not None:
-            _chk(residual, "residual")
         ws = workspace if workspace is not None and workspace.numel() >= nws else torch.empty(nws, dtype=torch.uint8, device=V.device)
         with torch.cuda.device(V.device):
             _lib.check(lib.wg2x2_conv_fwd_prepared_ws(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
@@ -126,10 +150,6 @@ def conv_fwd_prepared(V, prepared, K, out_h=None, out_w=None, layout="NHWC", out
             _lib.check(lib.wg2x2_conv_fwd_prepared(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
                                                    _stream()), "wg2x2_conv_fwd_prepared")
         else:
-            if residual is not None:
-                _chk(residual, "residual")
-                if residual.shape != Y.shape:
-                    raise ValueError("residual must have the shape of the output")
             _lib.check(lib.wg2x2_conv_fwd_prepared_fused(_ptr(V), _ptr(prepared), _ptr(Y), B, nH, nW, C, K, out_h, out_w, layout,
                                                          _ptr(out_scale), _ptr(out_shift), _ptr(residual), _stream()),
                        "wg2x2_conv_fwd_prepared_fused")
@@ -187,7 +207,12 @@ def layer_fwd_prepared(x, prepared, K, relu=True, layout="NHWC", out=None, V_scr
     layout = _LAYOUTS[layout]
     _chk(x, "x")
     B, H, W, C = _img_dims(x, layout)
-    Y = out if out is not None else torch.empty(_img_shape(B, H, W, K, layout), dtype=torch.float32, device=x.device)
+    _chk_prepared(prepared, C, K)
+    yshape = _img_shape(B, H, W, K, layout)
+    Y = _chk_shape(out, yshape, "out") if out is not None else torch.empty(yshape, dtype=torch.float32, device=x.device)
+    _chk_shape(out_scale, (K,), "out_scale"); _chk_shape(out_shift, (K,), "out_shift"); _chk_shape(residual, yshape, "residual")
+    if V_scratch is not None:
+        _chk_shape(V_scratch, (16, B, (H + 1) // 2, (W + 1) // 2, C), "V_scratch")
     if V_scratch is None and not lib.wg2x2_layer_fwd_fused_supported(B, H, W, C, K, layout):
         V_scratch = torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
@@ -203,7 +228,10 @@ def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shi
     per-input-channel affine map applied to the image in front of the transform (the padding stays zero)."""
     _chk(x, "x")
     B, C, H, W = x.shape
-    Y = out if out is not None else torch.empty((B, K, H, W), dtype=torch.float32, device=x.device)
+    _chk_prepared(prepared, C, K)
+    Y = _chk_shape(out, (B, K, H, W), "out") if out is not None else torch.empty((B, K, H, W), dtype=torch.float32, device=x.device)
+    _chk_shape(out_scale, (K,), "out_scale"); _chk_shape(out_shift, (K,), "out_shift"); _chk_shape(residual, (B, K, H, W), "residual")
+    _chk_shape(in_scale, (C,), "in_scale"); _chk_shape(in_shift, (C,), "in_shift")
     with torch.cuda.device(x.device):
         if in_scale is None and in_shift is None:
             _lib.check(lib.wg2x2_layer_fwd_fused(_ptr(x), _ptr(prepared), _ptr(Y), B, H, W, C, K, int(bool(relu)), _ptr(out_scale),
@@ -216,6 +244,9 @@ def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shi
 
 
 def last_device_status():
+    """(status, where) of the bounded device-side waits since the last reading; synchronises the current stream.
+    The tensor-core calls above do not read it themselves (that would cost a synchronisation per call): after a
+    time-out their outputs are incomplete, so a caller that must know polls here after its last launch."""
     import ctypes
     where = ctypes.c_uint(0)
     st = lib.wg2x2_last_device_status(_stream(), ctypes.byref(where))

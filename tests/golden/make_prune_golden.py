@@ -11,7 +11,9 @@ import sys
 
 import numpy as np
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2 and not os.environ.get("WG_REF"):
+    sys.exit("usage: python tests/golden/make_prune_golden.py <reference checkout>   (or WG_REF=<checkout>)")
+ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["WG_REF"]
 src = open(os.path.join(ref, "ResNet-18-var", "prune_script.py")).read().replace("\t", "    ")
 tree = ast.parse("\n".join(l for l in src.splitlines() if not l.strip().startswith("print ")))
 fn = next(n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "gen_prune_mask")

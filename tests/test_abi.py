@@ -65,6 +65,36 @@ def test_argument_validation_without_gpu(lib):
     assert b"workspace" in lib.wg2x2_status_string(-2)
 
 
+def test_misaligned_operands_are_refused_before_any_launch(lib):
+    """The tensor-core backward pass and the wide forward path use TMA and 16-byte accesses on every operand:
+    a pointer off a 16-byte boundary must come back as BAD_ARG, not reach a kernel.  The pointers here are
+    fake; the checks run before the first CUDA call, so this needs no GPU."""
+    P = ctypes.c_void_p
+    ok, off = P(4096), P(4096 + 4)
+    bwd = lib.wg2x2_conv_bwd
+    bwd.argtypes = [P] * 6 + [ctypes.c_int] * 8 + [P, ctypes.c_size_t, P]
+    B, H, W, C, K = 2, 8, 8, 64, 64
+    ws = P(1 << 20)
+    for bad in range(6):   # V, Wt, dY, mask, dV, dW in turn
+        ptrs = [off if i == bad else ok for i in range(6)]
+        assert bwd(*ptrs, B, H, W, C, K, 0, 1, 1, ws, 1 << 40, None) == -1, bad
+    fwd = lib.wg2x2_conv_fwd_prepared_ws
+    fwd.argtypes = [P] * 3 + [ctypes.c_int] * 8 + [P] * 3 + [P, ctypes.c_size_t, P]
+    C = K = 256
+    for bad in range(6):   # V, prepared, Y, out_scale, out_shift, residual
+        ptrs = [off if i == bad else ok for i in range(6)]
+        assert fwd(ptrs[0], ptrs[1], ptrs[2], B, 4, 4, C, K, 8, 8, 0, ptrs[3], ptrs[4], ptrs[5], ws, 1 << 40, None) == -1, bad
+
+
+def test_wait_limit_argument(lib):
+    f = lib.wg2x2_set_wait_limit
+    f.argtypes = [ctypes.c_longlong]
+    assert f(-5) == -1
+    assert f(1000) == 0
+    assert f(0) == 0          # back to the default
+    assert lib.wg2x2_test_drop_load(-1) == 0
+
+
 def test_workspace_queries(lib):
     q = lib.wg2x2_conv_bwd_workspace_bytes
     q.restype = ctypes.c_size_t

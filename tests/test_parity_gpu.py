@@ -118,6 +118,24 @@ def test_conv_bwd_fp32(wg, oracle, shape, use_mask, layout):
 
 
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_conv_bwd_fp32_conv5_width(wg, oracle, layout):
+    """The FP32 gradient kernels at the width of the conv5_x backward workload (C = K = 512, 7 x 7, a batch slice of 8):
+    dW runs split over the tiles with the deterministic reduction pass, dV with eight channel blocks."""
+    shape = (8, 7, 7, 512, 512)
+    B, H, W, C, K = shape
+    X, Wt, dY, mask = _inputs(shape)
+    Wt = Wt * mask
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    dVo, dWo = oracle.conv_bwd(V, Wt, dY, mask=mask)
+    assert wg._lib.lib.wg2x2_conv_bwd_workspace_bytes(B, H, W, C, K, 0, 1) > 0      # split-P scratch is in use
+    dV, dW = wg.conv_bwd(_dev(V), _dev(Wt), _dev(_to_layout(dY, layout)), mask=_dev(mask), layout=layout, relu=True)
+    _check(dV.cpu().numpy(), dVo * (V > 0), what="dV")
+    _check(dW.cpu().numpy(), dWo, what="dW")
+    dX = wg.imtrans_bwd(dV, H, W, layout=layout)
+    _check(_from_layout(dX, layout), oracle.imtrans_bwd(dVo * (V > 0), H, W), what="dX")
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 @pytest.mark.parametrize("use_mask", [False, True])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_imtrans_bwd(wg, oracle, shape, use_mask, layout):

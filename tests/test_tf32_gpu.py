@@ -92,9 +92,57 @@ def test_pruned_weights_and_block_skipping(wg, oracle):
     Yb = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, wide=False).cpu().numpy()   # the row-walk kernel, which skips blocks
     _status_ok(wg)
     assert oracle.max_rel(Yb, oracle.conv_fwd(V, Wb, H, W)) <= TOL_TF32
+    # the wide path (products as GEMMs with 256 output channels per unit) consults the same map
+    Yw = wg.conv_fwd_prepared(_dev(V), prepared, K, H, W, wide=True).cpu().numpy()
+    _status_ok(wg)
+    assert oracle.max_rel(Yw, oracle.conv_fwd(V, Wb, H, W)) <= TOL_TF32
     # all-zero weights: the output must be exactly zero, not stale accumulator contents
     Yz = wg.conv_fwd(_dev(V), _dev(np.zeros_like(Wt)), H, W, math="tf32")
     assert float(Yz.abs().max()) == 0.0
+    Yz = wg.conv_fwd_prepared(_dev(V), wg.prepare_weights(_dev(np.zeros_like(Wt))), K, H, W, wide=False)
+    assert float(Yz.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(2, 14, 14, 256, 256), (3, 8, 8, 320, 192), (2, 7, 7, 128, 64)])
+def test_block_skipping_in_the_gradient_products(wg, oracle, shape):
+    """dV on the tensor cores skips contraction chunks whose weight blocks are all zero (the map is rebuilt from the
+    weights on every call): block-structured, unstructured and all-zero weights must equal the dense arithmetic."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape, density=0.5)
+    rng = np.random.default_rng(5 + sum(shape))
+    dY = rng.standard_normal((B, H, W, K)).astype(np.float32)
+    V = oracle.imtrans_fwd(X, relu=True, dtype=np.float32)
+    blocks = rng.random((16, (C + 31) // 32, (K + 63) // 64)) < 0.4
+    blocks[:, :, 0] |= rng.random((16, (C + 31) // 32)) < 0.5
+    Wb = Wt * np.repeat(np.repeat(blocks, 32, axis=1), 64, axis=2)[:, :C, :K]
+    for Wc in (Wb, Wt, np.zeros_like(Wt)):
+        dV, _ = wg.conv_bwd(_dev(V), _dev(Wc), _dev(dY), math="tf32", need_dW=False)
+        _status_ok(wg)
+        want = oracle.conv_bwd(V, Wc, dY)[0]
+        if not Wc.any():
+            assert float(dV.abs().max()) == 0.0
+        else:
+            assert oracle.max_rel(dV.cpu().numpy(), want) <= TOL_TF32
+
+
+@pytest.mark.parametrize("shape", [(2, 16, 16, 128, 128), (1, 28, 28, 256, 64), (3, 8, 12, 96, 192)])
+def test_block_skipping_in_the_one_kernel_layer(wg, oracle, shape):
+    """The one-kernel layer's MMA issuers leave out the weight tiles the zero-block map marks empty."""
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape, density=0.5)
+    rng = np.random.default_rng(7 + sum(shape))
+    blocks = rng.random((16, (C + 31) // 32, (K + 63) // 64)) < 0.4
+    blocks[:, 0, :] |= rng.random((16, (K + 63) // 64)) < 0.5
+    Wb = Wt * np.repeat(np.repeat(blocks, 32, axis=1), 64, axis=2)[:, :C, :K]
+    Xc = _dev(np.ascontiguousarray(np.transpose(X, (0, 3, 1, 2))))
+    V = oracle.imtrans_fwd(X, relu=True)
+    for Wc in (Wb, np.zeros_like(Wt)):
+        Y = wg.layer_fwd_fused(Xc, wg.prepare_weights(_dev(Wc)), K, relu=True)
+        _status_ok(wg)
+        if not Wc.any():
+            assert float(Y.abs().max()) == 0.0
+        else:
+            assert oracle.max_rel(np.transpose(Y.cpu().numpy(), (0, 2, 3, 1)), oracle.conv_fwd(V, Wc, H, W)) <= TOL_TF32
 
 
 def test_prepared_weights_reused(wg, oracle):
@@ -294,6 +342,30 @@ def test_fused_many_units_per_cta_repeated(wg, oracle, shape, launches):
     want = oracle.conv_fwd(oracle.imtrans_fwd(xs, relu=True), Wt.cpu().numpy(), H, W)
     got = np.transpose(first[0][:2].cpu().numpy(), (0, 2, 3, 1))
     assert oracle.max_rel(got, want) <= TOL_TF32
+
+
+@pytest.mark.parametrize("layout", ["NCHW", "NHWC"])
+def test_two_kernel_path_at_full_conv2_batch(wg, oracle, layout):
+    """Input transform + product kernel at the full batch of the conv2_x workload (64 x 64 x 56 x 56, K = 64), where
+    the product kernel shrinks its units so that they divide evenly over the SMs: sampled images against the
+    float64 oracle, every image against the one-kernel path."""
+    B, H, W, C, K = 64, 56, 56, 64, 64
+    gen = torch.Generator(device="cuda").manual_seed(17)
+    X = torch.randn((B, C, H, W), generator=gen, device="cuda")
+    Wt = 0.05 * torch.randn((16, C, K), generator=gen, device="cuda")
+    prepared = wg.prepare_weights(Wt)
+    xin = X if layout == "NCHW" else X.permute(0, 2, 3, 1).contiguous()
+    V = wg.imtrans_fwd(xin, relu=True, layout=layout)
+    Y = wg.conv_fwd_prepared(V, prepared, K, H, W, layout=layout)
+    _status_ok(wg)
+    Yn = Y if layout == "NHWC" else Y.permute(0, 2, 3, 1)
+    for b in (0, 17, 38, 63):        # first, last and two images whose tiles straddle unit boundaries
+        xs = np.ascontiguousarray(X[b:b + 1].permute(0, 2, 3, 1).cpu().numpy())
+        want = oracle.conv_fwd(oracle.imtrans_fwd(xs, relu=True), Wt.cpu().numpy(), H, W)
+        assert oracle.max_rel(Yn[b:b + 1].cpu().numpy(), want) <= TOL_TF32, b
+    Yf = wg.layer_fwd_fused(X, prepared, K, relu=True)
+    assert oracle.max_rel(Yn.permute(0, 3, 1, 2).cpu().numpy(), Yf.cpu().numpy()) <= 2e-3
+    _status_ok(wg)
 
 
 def test_layer_fwd_prepared_falls_back_to_two_kernels(wg, oracle):

@@ -54,6 +54,8 @@ def test_noalloc_matches_workspace_entry_point_twice(layout, shape):
             assert free_after >= free_before - (1 << 20), "the entry point must not allocate device memory"
         assert torch.isfinite(got).all()
         assert _max_rel(got, want) <= TOL, "call %d" % call
+        # same split count and the same order of additions as the workspace entry point: the very same bits
+        assert torch.equal(got, want), "call %d" % call
 
 
 def test_noalloc_rejects_sizes_beyond_the_builtin_scratch():
