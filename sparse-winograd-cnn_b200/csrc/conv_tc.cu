@@ -101,6 +101,17 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, ok);
 }
 
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
 {
     asm volatile(
@@ -256,7 +267,8 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     unsigned long long *role_masks = reinterpret_cast<unsigned long long *>(bars_gen + 2 * kStages + 8);  // 2 x 16 words
     float *epi_stage_all = reinterpret_cast<float *>(gen_base + kStages * kStageBytes + kCtrlBytes);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // (broadcast from lane 0: the compiler then treats the warp index, and all that is derived from it, as warp-uniform)
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -271,7 +283,7 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr_slot;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_slot, 0);
 
     const int nCC = prm.nCC;
 
@@ -314,19 +326,25 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------------
-        if (lane == 0) {
+        // The whole warp walks the loop with warp-uniform values, so that descriptors and addresses live in uniform
+        // registers; one elected lane issues the MMAs and the commits.  (Issued by a lone lane from per-thread
+        // registers, an MMA takes several times as many issue slots, and the epilogue warps compete for them.)
+        {
             constexpr uint32_t idesc = make_idesc_tf32(kBlockM, kBlockN);
+            const bool leader = elect_one();
             int s = 0; uint32_t ph = 0;
             uint32_t acc_use[2] = {0, 0};
             bool ok = true;
             int tr = 0; (void)tr;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 const int kb = u % prm.nKB;
-                load_unit_masks(prm.masks, prm.nKB, kb, role_masks + 16);
+                __syncwarp();
+                if (lane < 16) role_masks[16 + lane] = __ldg(prm.masks + (long long)lane * prm.nKB + kb);
+                __syncwarp();
                 for (int i = 0; i < 4 && ok; ++i) {
                     const int buf = i & 1;
                     // the epilogue must have drained this accumulator buffer
-                    if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf, prm.spin_limit)) { ok = false; break; }
+                    if (!mbar_wait_warp(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x200u | buf, prm.spin_limit)) { ok = false; break; }
                     acc_use[buf]++;
                     tc_fence_after();
                     for (int j = 0; j < 4 && ok; ++j) {
@@ -335,21 +353,26 @@ conv_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
                         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 4 * kBlockN + j * kBlockN);
                         for (int cc = 0; cc < nCC; ++cc) {
                             if (cc > 0 && cc < 64 && !((mk >> cc) & 1ull)) continue;
-                            if (!mbar_wait(full_bar(s), ph, abort_flag, 0x300u | s, prm.spin_limit)) { ok = false; break; }
-                            TC_TRACE(512 + tr);
+                            if (!mbar_wait_warp(full_bar(s), ph, abort_flag, 0x300u | s, prm.spin_limit)) { ok = false; break; }
+                            if (leader) TC_TRACE(512 + tr);
                             tc_fence_after();
                             const uint32_t a_addr = base + s * kStageBytes;
                             const uint64_t adesc = make_desc_k_sw128(a_addr);
                             const uint64_t bdesc = make_desc_k_sw128(a_addr + kABytes);
+                            if (leader) {
 #pragma unroll
-                            for (int kk = 0; kk < kBlockK / 8; ++kk)   // 32 bytes (8 tf32) further along K per step
-                                umma_tf32(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (cc > 0 || kk > 0) ? 1u : 0u);
-                            umma_commit(empty_bar(s));
-                            TC_TRACE(1024 + tr); ++tr;
+                                for (int kk = 0; kk < kBlockK / 8; ++kk)   // 32 bytes (8 tf32) further along K per step
+                                    umma_tf32(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (cc > 0 || kk > 0) ? 1u : 0u);
+                                umma_commit(empty_bar(s));
+                            }
+                            __syncwarp();
+                            if (leader) TC_TRACE(1024 + tr);
+                            ++tr;
                             if (++s == kStages) { s = 0; ph ^= 1u; }
                         }
                     }
-                    if (ok) umma_commit(accf_bar(buf));
+                    if (ok && leader) umma_commit(accf_bar(buf));
+                    __syncwarp();
                 }
             }
         }

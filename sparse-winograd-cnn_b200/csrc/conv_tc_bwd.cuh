@@ -336,7 +336,8 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + 2 * kGgStages + 5);
     float *epi_stage_all = reinterpret_cast<float *>(gen_base + kGgStages * kGgStageBytes + kCtrlBytes);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // (broadcast from lane 0: the compiler then treats the warp index, and all that is derived from it, as warp-uniform)
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGgStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(accf_bar(b), 1); mbar_init(acce_bar(b), kEpiWarps); }
@@ -350,7 +351,7 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr_slot;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_slot, 0);
 
     const int N = prm.N;
     // unit -> (split, t, row block, column block); column block fastest so that neighbouring CTAs share the A tile in L2
@@ -395,7 +396,11 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                 for (int it = 0; it < 1000; ++it) __nanosleep(1000);
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp walks the loop with warp-uniform values (descriptors and addresses in uniform registers); one
+        // elected lane issues the MMAs and the commits.  Issued by a lone lane from per-thread registers, an MMA costs
+        // several times as many issue slots, for which the eight epilogue warps compete.
+        {
+            const bool leader = elect_one();
             const uint32_t idesc = make_idesc_tf32(128, N) | (KIND == 0 ? ((1u << 15) | (1u << 16)) : 0u);
             int s = 0; uint32_t ph = 0;
             uint32_t acc_use[2] = {0, 0};
@@ -406,7 +411,7 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                 decode(u, split, t, rb, cb);
                 const long long kbeg = (long long)split * prm.chunks_per_split * 32;
                 const long long kend = min(prm.contr, kbeg + (long long)prm.chunks_per_split * 32);
-                if (!mbar_wait(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x600u | buf)) { ok = false; break; }
+                if (!mbar_wait_warp(acce_bar(buf), (acc_use[buf] & 1u) ^ 1u, abort_flag, 0x600u | buf)) { ok = false; break; }
                 acc_use[buf]++;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 256);
@@ -414,21 +419,24 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                 const unsigned long long live = KIND == 1 ? gg_live_chunks(prm, t, cb) : ~0ull;
                 for (long long kc = kbeg; kc < kend; kc += 32) {
                     if (KIND == 1 && kc < 64 * 32 && !((live >> (kc >> 5)) & 1ull)) continue;
-                    if (!mbar_wait(full_bar(s), ph, abort_flag, 0x700u | s)) { ok = false; break; }
+                    if (!mbar_wait_warp(full_bar(s), ph, abort_flag, 0x700u | s)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = base + s * kGgStageBytes;
                     const uint64_t adesc = KIND == 0 ? make_desc_mn_sw128(a_addr) : make_desc_k_sw128(a_addr);
                     const uint64_t bdesc = KIND == 0 ? make_desc_mn_sw128(a_addr + kGgABytes) : make_desc_k_sw128(a_addr + kGgABytes);
                     const uint32_t step = KIND == 0 ? 64u : 2u;   // 1024 B / 32 B per 8 contraction steps
+                    if (leader) {
 #pragma unroll
-                    for (int kg = 0; kg < 4; ++kg) {
-                        umma_tf32(d_tmem, adesc + step * kg, bdesc + step * kg, idesc, first ? 0u : 1u);
-                        first = 0;
+                        for (int kg = 0; kg < 4; ++kg)
+                            umma_tf32(d_tmem, adesc + step * kg, bdesc + step * kg, idesc, (first && kg == 0) ? 0u : 1u);
+                        umma_commit(empty_bar(s));
                     }
-                    umma_commit(empty_bar(s));
+                    __syncwarp();
+                    first = 0;
                     if (++s == kGgStages) { s = 0; ph ^= 1u; }
                 }
-                if (ok) umma_commit(accf_bar(buf));
+                if (ok && leader) umma_commit(accf_bar(buf));
+                __syncwarp();
                 buf ^= 1;
             }
         }

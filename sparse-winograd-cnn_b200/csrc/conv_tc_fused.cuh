@@ -201,7 +201,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
     constexpr int kB0 = 0, kB1 = kB0 + kFuAGroups, kB4 = kB1 + kFuAGroups,
                   kB5 = kB4 + 2, kB6 = kB5 + 2, kB7 = kB6 + kFuXfull, kB7b = kB7 + kFuXbufs, kB8 = kB7b + 4;
-    static_assert((kB8 + 2) <= 32 && (32 + 4 * 16) * 8 <= kCtrlBytes, "control block: barriers, then the issuers' zero-block words");
+    static_assert((kB8 + 3) <= 32 && (32 + 4 * 16) * 8 <= kCtrlBytes, "control block: barriers, then the issuers' zero-block words");
     auto full_bar = [&](int g) { return bars + 8u * (kB0 + g); };
     auto free_bar = [&](int g) { return bars + 8u * (kB1 + g); };
     auto accf_bar = [&](int b) { return bars + 8u * (kB4 + b); };
@@ -212,8 +212,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     auto yfree_bar = [&](int h) { return bars + 8u * (kB7b + 2 + h); };
     volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + kB8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + kB8 + 1);
+    volatile int *team_ok = reinterpret_cast<volatile int *>(bars_gen + kB8 + 2);   // [2]: verdict of a team's polling warp
+    (void)team_ok;
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // (broadcast from lane 0: the compiler then treats the warp index, and all that is derived from it, as warp-uniform)
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     FU_CTA_STAMP(0);
 
     if (threadIdx.x == 0) {
@@ -232,7 +235,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_ptr_slot;
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_ptr_slot, 0);
     FU_CTA_STAMP(1);
     // Launched with programmatic stream serialisation, this grid may have been scheduled while the kernel before it in
     // the stream was still running (on SMs that one left free, or as its CTAs ended): everything up to here touched
@@ -252,13 +255,17 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     // registers: 1024 threads x 64 at launch; control warps keep 32, epilogue warps stay at 64, transform warps take 80
     if (warp < 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFuRegsCtrl));
-        if (warp < 4 && lane == 0) {
+        if (warp < 4) {
             // ------------------------------ MMA issuers -----------------------------------
             // Issuer (a, e) = warp (2a + e) owns that accumulator: position (i, j) goes into it with the sign
             // At[a][i] * At[e][j]; At = [[1,1,1,0],[0,1,-1,-1]], so column e takes j = e..e+2 and row a takes
             // i = a..a+2.  On the one row it has nothing to add the issuer still follows the ring (wait, commit).
+            // The whole warp walks the loop with warp-uniform values (warp index and tensor-memory base were
+            // broadcast from lane 0), so that descriptors and addresses live in uniform registers; one elected lane
+            // issues the MMAs and the commits.
             constexpr uint32_t idesc_pos = make_idesc_tf32(kBlockM, kBlockN);
             constexpr uint32_t idesc_neg = idesc_pos | (1u << 14);            // negate B
+            const bool leader = elect_one();
             const int a = warp >> 1, e = warp & 1;
             const uint32_t d_tmem = tmem_base + (uint32_t)(warp * kBlockN);
             const uint32_t a_tmem0 = tmem_base + (uint32_t)(kFuACol0 + e * 32);
@@ -274,40 +281,53 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             // input channels cc*32.., holds a non-zero)
             unsigned long long *my_masks = reinterpret_cast<unsigned long long *>(bars_gen + 32 + warp * 16);
             const uint32_t *my_masks32 = reinterpret_cast<const uint32_t *>(my_masks);
+            bool dense = true;
             for (int n = 0; n < total; ++n) {
                 if (cc == 0 && i == 0) {
                     int gu, rbu, segu, kbu;
                     decode((int)blockIdx.x + (int)units_done * (int)gridDim.x, gu, rbu, segu, kbu);
-                    load_unit_masks(prm.masks, prm.nKB, kbu, my_masks);
+                    unsigned long long all = ~0ull;
+                    if (lane < 16) {
+                        all = __ldg(prm.masks + (long long)lane * prm.nKB + kbu);
+                        my_masks[lane] = all;
+                    }
+                    const unsigned long long need = nC32 >= 64 ? ~0ull : ((1ull << nC32) - 1ull);
+                    dense = __all_sync(0xffffffffu, (all & need) == need);   // the common case: no block of this unit is empty
                 }
-                if (warp == 0) TC_TRACE(1024 + 5 * trm);
-                if (!mbar_wait(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g, prm.spin_limit)) break;
-                if (warp == 0) TC_TRACE(1024 + 5 * trm + 1);
+                if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm);
+                if (!mbar_wait_warp(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g, prm.spin_limit)) break;
+                if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm + 1);
                 // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
-                if (cc == 0 && i == a && !mbar_wait(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a, prm.spin_limit)) break;
-                if (warp == 0) TC_TRACE(1024 + 5 * trm + 2);
+                if (cc == 0 && i == a && !mbar_wait_warp(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a, prm.spin_limit)) break;
+                if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm + 2);
                 tc_fence_after();
                 int g2 = g + 1; uint32_t gph2 = gph;
                 if (g2 == kFuAGroups) { g2 = 0; gph2 ^= 1u; }
-                if (i >= a && i <= a + 2) {
+                const bool active = i >= a && i <= a + 2;
+                if (active) {
                     const bool neg_a = (a == 1 && i >= 2);
                     const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
 #pragma unroll
                     for (int jj = 0; jj < 3; ++jj) {
                         // an all-zero weight tile adds nothing (the slot's first chunk always runs: it zero-initialises)
-                        if (cc > 0 && cc < 64 && !((my_masks32[2 * (4 * i + e + jj) + (cc >> 5)] >> (cc & 31)) & 1u)) continue;
+                        if (!dense && cc > 0 && cc < 64 && !((my_masks32[2 * (4 * i + e + jj) + (cc >> 5)] >> (cc & 31)) & 1u)) continue;
                         const bool neg_e = (e == 1 && jj >= 1);                      // At[1][j] = -1 for j = 2, 3
                         const uint32_t idesc = (neg_a != neg_e) ? idesc_neg : idesc_pos;
                         const uint32_t aj = a_tmem + (uint32_t)(jj * 32), bj = b_lo + (uint32_t)(jj * (kFuWTile >> 4));
-                        umma_tf32_ts_x2(d_tmem, aj, bj, b_hi, idesc, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
-                        umma_tf32_ts_x2(d_tmem, aj + 16u, bj + 4u, b_hi, idesc, 1u);
+                        if (leader) {
+                            umma_tf32_ts_x2(d_tmem, aj, bj, b_hi, idesc, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
+                            umma_tf32_ts_x2(d_tmem, aj + 16u, bj + 4u, b_hi, idesc, 1u);
+                        }
                     }
                 }
-                if (warp == 0) TC_TRACE(1024 + 5 * trm + 3);
-                // (an issuer that added nothing in this slot has nothing for a commit to track: it arrives directly)
-                if (i >= a && i <= a + 2) umma_commit(free_bar(g)); else mbar_arrive(free_bar(g));
-                if (cc == nC32 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
-                if (warp == 0) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
+                if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm + 3);
+                if (leader) {
+                    // (an issuer that added nothing in this slot has nothing for a commit to track: it arrives directly)
+                    if (active) umma_commit(free_bar(g)); else mbar_arrive(free_bar(g));
+                    if (cc == nC32 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
+                }
+                __syncwarp();
+                if (warp == 0 && leader) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
                 g = g2; gph = gph2;
                 if (++cc == nC32) { cc = 0; if (++i == 4) { i = 0; ++units_done; } }
             }
@@ -439,10 +459,30 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             // both waits, then one vote (the warp converged and of one mind before the aligned instructions below)
+#if defined(WG_FU_TEAM_POLL)
+            // one warp of the team polls the two barriers; the other seven wait for it at a named barrier, where they
+            // take no issue slots from the warps that have work
+            bool got_a = true;
+            if (tw8 == 0) {
+                const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, prm.spin_limit);
+                got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, prm.spin_limit);
+                got_a = __all_sync(0xffffffffu, got_a);
+                if (lane == 0) team_ok[team] = got_a ? 1 : 0;
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "n"(32 * kFuTeamWarps) : "memory");
+            got_a = team_ok[team] != 0;
+            if (!got_a) { ok = false; break; }
+#elif defined(WG_FU_XF_SLEEP)
+            const bool got_x = mbar_wait_sleepy(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, WG_FU_XF_SLEEP, prm.spin_limit);
+            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
+            const bool got_a = got_x && mbar_wait_sleepy(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, WG_FU_XF_SLEEP, prm.spin_limit);
+            if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
+#else
             const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, prm.spin_limit);
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
             const bool got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, prm.spin_limit);
             if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
+#endif
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
             const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
