@@ -174,7 +174,8 @@ size_t wg2x2_layer_fwd_workspace_bytes(int B, int H, int W, int C, int K, int ma
 
 /*
  * Whole layer forward with prepared weights (tensor-core path), the call pair of
- * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119 in its fastest form for the shape:
+ * ResNet-18-var/imagenet-resnet-transWino-prune.py:118-119 in its fastest form for the shape that needs no scratch
+ * memory beyond V_scratch (wg2x2_layer_fwd_prepared_ws adds the wide path for C, K >= 256):
  *  - one kernel (wg2x2_layer_fwd_fused) where that is supported (NCHW, W % 4 == 0, C % 16 == 0, X and Y
  *    16-byte aligned) and either it is the faster one (K <= 128, or K <= 256 with C <= 64) or no V_scratch
  *    was given: both transforms and the ReLU happen on the SM, neither the transformed input nor the
@@ -185,6 +186,16 @@ size_t wg2x2_layer_fwd_workspace_bytes(int B, int H, int W, int C, int K, int ma
 int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, float *V_scratch, int B, int H, int W,
                              int C, int K, int layout, int relu, const float *out_scale, const float *out_shift,
                              const float *residual, void *stream);
+/*
+ * The same with scratch memory for the products, which lets layers with many channels (C, K >= 256) take their
+ * fastest form too: input transform into V_scratch, then the wide path of wg2x2_conv_fwd_prepared_ws through
+ * `workspace` (wg2x2_layer_fwd_prepared_workspace_bytes; 0 = the shape does not use one).  With workspace == NULL, or
+ * for other shapes, this is wg2x2_layer_fwd_prepared.
+ */
+int wg2x2_layer_fwd_prepared_ws(const float *X, const void *prepared, float *Y, float *V_scratch, int B, int H, int W,
+                                int C, int K, int layout, int relu, const float *out_scale, const float *out_shift,
+                                const float *residual, void *workspace, size_t workspace_bytes, void *stream);
+size_t wg2x2_layer_fwd_prepared_workspace_bytes(int B, int H, int W, int C, int K);
 int wg2x2_layer_fwd_fused_supported(int B, int H, int W, int C, int K, int layout);
 /* The one-kernel layer forward on its own (NCHW in and out); WG2X2_ERR_UNSUPPORTED outside the shapes above.
  * residual may be Y itself: the result is then added into Y in place (the TMA unit does the addition);

@@ -231,6 +231,29 @@ int wg2x2_layer_fwd_prepared(const float *X, const void *prepared, float *Y, flo
     return conv_fwd_tc_prepared(V_scratch, prepared, Y, B, nH, nW, C, K, H, W, layout, out_scale, out_shift, residual, st);
 }
 
+size_t wg2x2_layer_fwd_prepared_workspace_bytes(int B, int H, int W, int C, int K)
+{
+    if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return 0;
+    return wg2x2_conv_fwd_prepared_workspace_bytes(B, (H + 1) / 2, (W + 1) / 2, C, K);
+}
+
+int wg2x2_layer_fwd_prepared_ws(const float *X, const void *prepared, float *Y, float *V_scratch, int B, int H, int W, int C, int K,
+                                int layout, int relu, const float *out_scale, const float *out_shift, const float *residual,
+                                void *workspace, size_t workspace_bytes, void *stream)
+{
+    if (!X || !prepared || !Y || B <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return WG2X2_ERR_BAD_ARG;
+    if (!layout_ok(layout)) return WG2X2_ERR_BAD_ARG;
+    // layers with many channels: input transform, then the products as wide GEMMs through the workspace
+    if (conv_fwd_wide_preferred(C, K) && V_scratch && workspace) {
+        const int nH = (H + 1) / 2, nW = (W + 1) / 2;
+        const int s = imtrans_fwd(X, V_scratch, B, H, W, C, layout, relu, nullptr, nullptr, (cudaStream_t)stream);
+        if (s != WG2X2_OK) return s;
+        return wg2x2_conv_fwd_prepared_ws(V_scratch, prepared, Y, B, nH, nW, C, K, H, W, layout, out_scale, out_shift, residual, workspace,
+                                          workspace_bytes, stream);
+    }
+    return wg2x2_layer_fwd_prepared(X, prepared, Y, V_scratch, B, H, W, C, K, layout, relu, out_scale, out_shift, residual, stream);
+}
+
 int wg2x2_layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H, int W, int C, int K, int relu,
                           const float *out_scale, const float *out_shift, const float *residual, void *stream)
 {

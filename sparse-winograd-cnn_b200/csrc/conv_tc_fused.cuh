@@ -168,11 +168,21 @@ __device__ __forceinline__ float2 lds_f2(uint32_t addr)
     asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
     return v;
 }
-// 4 registers per thread -> this warp's 32 lanes x 4 consecutive 32-bit columns
+// 4 registers per thread -> this warp's 32 lanes x 4 consecutive 32-bit columns.
+// The tensor core reads the upper 19 bits of each value (TF32) and drops the rest, as it does for V that the
+// two-kernel path brings from memory.  Built with -DWG2X2_ROUND_V, half a unit of the last kept place is added to
+// the bit pattern first, which turns that truncation into rounding to nearest (magnitude-wise, as cvt.rna.tf32
+// does) and removes the one-sided bias of about 2^-12 per product; it costs one integer add per value, measured
+// 1.8 % of the kernel's time on the 64 x 64 x 56 x 56 layer, and is off by default.
+#ifdef WG2X2_ROUND_V
+#define WG_FU_RND(x) (__float_as_uint(x) + 0x1000u)
+#else
+#define WG_FU_RND(x) __float_as_uint(x)
+#endif
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, const float *r)
 {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};"
-                 ::"r"(taddr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3]))
+                 ::"r"(taddr), "r"(WG_FU_RND(r[0])), "r"(WG_FU_RND(r[1])), "r"(WG_FU_RND(r[2])), "r"(WG_FU_RND(r[3]))
                  : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -512,15 +522,23 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         }
                     }
 #endif
+#ifdef WG_KO_LDS   // development knock-out: no shared-memory loads (results wrong)
+                    const float2 am = make_float2((float)cq, sb), bm = make_float2(sb, (float)q);
+#else
                     const float2 am = lds_f2(xq_s + (uint32_t)(4 * (c4 * 4 + cq) * chs));
                     const float2 bm = lds_f2(xq_s + (uint32_t)(4 * ((c4 * 4 + cq) * chs + dab)));
+#endif
                     const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
+#ifdef WG_KO_SHFL  // development knock-out: no shuffles (results wrong)
+                    float r0 = r2 * 0.5f, r3 = r1 * 0.25f;
+#else
                     float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
+#endif
                     if (!kByLanes) {
                         if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
                         if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
                     }
-                    // written as fp32: the tensor core reads the upper 19 bits (TF32), as it does for V from memory
+                    // (fp32 values; what the tensor core makes of the low mantissa bits: see tmem_st4)
                     if (AFFINE) {
                         const float sc = sc8[q * 4 + cq], tc = tc8[q * 4 + cq];
                         o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * RC0), lo);
@@ -535,7 +553,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     }
                 }
 #pragma unroll
+#ifdef WG_KO_ST    // development knock-out: one tensor-memory store instead of four (results wrong)
+                { float z[4] = {o[0][0] + o[1][1], o[2][2] + o[3][3], o[0][1] + o[1][2], o[2][3] + o[3][0]}; tmem_st4(a_tmem + (uint32_t)(c4 * 4), z); }
+#else
                 for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
+#endif
                 if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
             }
             };

@@ -50,6 +50,8 @@ _SIGS = {
     "wg2x2_layer_fwd": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p, _z, _p]),
     "wg2x2_layer_fwd_workspace_bytes": (_z, [_i, _i, _i, _i, _i, _i, _i]),
     "wg2x2_layer_fwd_prepared": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
+    "wg2x2_layer_fwd_prepared_ws": (_i, [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _z, _p]),
+    "wg2x2_layer_fwd_prepared_workspace_bytes": (_z, [_i, _i, _i, _i, _i]),
     "wg2x2_layer_fwd_fused": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]),
     "wg2x2_layer_fwd_fused_affine": (_i, [_p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _p]),
     "wg2x2_layer_fwd_fused_supported": (_i, [_i, _i, _i, _i, _i, _i]),

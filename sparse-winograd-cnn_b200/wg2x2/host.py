@@ -70,6 +70,8 @@ class HostLayerPipeline:
             biggest = max(hi - lo for lo, hi in self.bounds)
             self.vflat = [torch.empty(16 * biggest * nH * nW * C, device=self.device) for _ in range(2)]
             self.vshape = lambda n: (16, n, nH, nW, C)
+            nws = ops.layer_fwd_prepared_workspace_bytes(biggest, H, W, C, K) if math == "tf32" else 0
+            self.ws = torch.empty(nws, dtype=torch.uint8, device=self.device) if nws else None   # products of the wide path
             self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
             self.ev_in = [torch.cuda.Event() for _ in self.bounds]
             self.ev_run = [torch.cuda.Event() for _ in self.bounds]
@@ -113,7 +115,7 @@ class HostLayerPipeline:
                 if prepared is not None:
                     # the library picks the one-kernel path where it pays (v is then unused), else the two kernels
                     ops.layer_fwd_prepared(self.xd[i], prepared, self.K, relu=self.relu, layout=self.layout, out=self.yd[i],
-                                           V_scratch=v)
+                                           V_scratch=v, workspace=self.ws)
                 else:
                     ops.imtrans_fwd(self.xd[i], relu=self.relu, layout=self.layout, out=v)
                     ops.conv_fwd(v, Wt, self.H, self.W, layout=self.layout, math=self.math, out=self.yd[i])

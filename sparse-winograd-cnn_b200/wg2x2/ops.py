@@ -201,9 +201,10 @@ def fused_supported(B, H, W, C, K, layout="NCHW"):
 
 
 def layer_fwd_prepared(x, prepared, K, relu=True, layout="NHWC", out=None, V_scratch=None, out_scale=None, out_shift=None,
-                       residual=None):
+                       residual=None, workspace=None):
     """Whole layer with prepared weights: one fused kernel where supported (V never stored), else transform +
-    product through V_scratch (allocated here when not given)."""
+    product through V_scratch (allocated here when not given); layers with C, K >= 256 take the wide product path
+    through `workspace` (allocated here when not given; layer_fwd_prepared_workspace_bytes)."""
     layout = _LAYOUTS[layout]
     _chk(x, "x")
     B, H, W, C = _img_dims(x, layout)
@@ -213,13 +214,21 @@ def layer_fwd_prepared(x, prepared, K, relu=True, layout="NHWC", out=None, V_scr
     _chk_shape(out_scale, (K,), "out_scale"); _chk_shape(out_shift, (K,), "out_shift"); _chk_shape(residual, yshape, "residual")
     if V_scratch is not None:
         _chk_shape(V_scratch, (16, B, (H + 1) // 2, (W + 1) // 2, C), "V_scratch")
-    if V_scratch is None and not lib.wg2x2_layer_fwd_fused_supported(B, H, W, C, K, layout):
+    nws = lib.wg2x2_layer_fwd_prepared_workspace_bytes(B, H, W, C, K)
+    if V_scratch is None and (nws or not lib.wg2x2_layer_fwd_fused_supported(B, H, W, C, K, layout)):
         V_scratch = torch.empty((16, B, (H + 1) // 2, (W + 1) // 2, C), dtype=torch.float32, device=x.device)
+    if nws and (workspace is None or workspace.numel() < nws):
+        workspace = torch.empty(nws, dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        _lib.check(lib.wg2x2_layer_fwd_prepared(_ptr(x), _ptr(prepared), _ptr(Y), _ptr(V_scratch), B, H, W, C, K, layout,
-                                                int(bool(relu)), _ptr(out_scale), _ptr(out_shift), _ptr(residual), _stream()),
-                   "wg2x2_layer_fwd_prepared")
+        _lib.check(lib.wg2x2_layer_fwd_prepared_ws(_ptr(x), _ptr(prepared), _ptr(Y), _ptr(V_scratch), B, H, W, C, K, layout,
+                                                   int(bool(relu)), _ptr(out_scale), _ptr(out_shift), _ptr(residual),
+                                                   _ptr(workspace) if nws else None, nws, _stream()),
+                   "wg2x2_layer_fwd_prepared_ws")
     return Y
+
+
+def layer_fwd_prepared_workspace_bytes(B, H, W, C, K):
+    return int(lib.wg2x2_layer_fwd_prepared_workspace_bytes(B, H, W, C, K))
 
 
 def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shift=None, residual=None,

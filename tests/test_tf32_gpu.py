@@ -379,6 +379,25 @@ def test_layer_fwd_prepared_falls_back_to_two_kernels(wg, oracle):
 
 
 @pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
+def test_layer_fwd_prepared_takes_the_wide_path(wg, oracle, layout):
+    """The whole-layer call with prepared weights: for C, K >= 256 it asks for product scratch and gives the result of the
+    wide path (bit for bit what input transform + conv_fwd_prepared give)."""
+    shape = (4, 14, 14, 256, 256)
+    B, H, W, C, K = shape
+    X, Wt = _inputs(shape)
+    assert wg.layer_fwd_prepared_workspace_bytes(B, H, W, C, K) == 16 * B * 7 * 7 * K * 4
+    assert wg.layer_fwd_prepared_workspace_bytes(B, 56, 56, 64, 64) == 0
+    x = _dev(X if layout == "NHWC" else np.ascontiguousarray(np.transpose(X, (0, 3, 1, 2))))
+    prepared = wg.prepare_weights(_dev(Wt))
+    Y = wg.layer_fwd_prepared(x, prepared, K, relu=True, layout=layout)
+    _status_ok(wg)
+    V = wg.imtrans_fwd(x, relu=True, layout=layout)
+    assert torch.equal(Y, wg.conv_fwd_prepared(V, prepared, K, H, W, layout=layout, wide=True))
+    got = Y.cpu().numpy() if layout == "NHWC" else np.transpose(Y.cpu().numpy(), (0, 2, 3, 1))
+    assert oracle.max_rel(got, oracle.conv_fwd(oracle.imtrans_fwd(X, relu=True), Wt, H, W)) <= TOL_TF32
+
+
+@pytest.mark.parametrize("layout", ["NHWC", "NCHW"])
 @pytest.mark.parametrize("shape", [(3, 14, 14, 256, 256), (16, 7, 7, 512, 512), (2, 9, 13, 260, 264), (1, 28, 28, 256, 320)])
 def test_wide_forward_path(wg, oracle, shape, layout):
     """Layers with many channels: products as wide GEMMs into scratch memory + output transform pass, against the
