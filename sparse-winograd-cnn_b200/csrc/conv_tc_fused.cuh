@@ -2,7 +2,7 @@
 // nor the 16 Winograd-domain products ever exist outside the SM.  Included by conv_tc.cu.
 //
 // Both transforms ride on the tensor core's operands:
-//   * input side: the A operand of every MMA (row i, column j of B^T d B for 128 tiles x 8 channels, after
+//   * input side: the A operand of every MMA (position (i, j) of B^T d B for 128 tiles x 8 channels, after
 //     the ReLU) is computed by the transform warps and written with tcgen05.st into tensor memory
 //     (lane = tile, column = channel); tcgen05.mma reads it from there;
 //   * output side: y[a][e] = sum_ij At[a][i] At[e][j] (V_ij . W_ij) is linear in the products and the
@@ -10,48 +10,60 @@
 //     accumulators (a, e) it contributes to, with the instruction descriptor's negate bit for the minus
 //     signs.  That costs 36 instead of 16 MMAs per 8 channels (the tensor core has the room) and leaves four
 //     128x64 accumulators per unit instead of sixteen products: the epilogue only copies.
-// A ring slot = one Winograd row i of one block of tiles for 32 input channels (four [128 x 32] A tiles in
-// tensor memory + four [64 x 32] weight tiles in shared memory); a step = one 16-channel half of a slot:
+// A unit walks the Winograd rows in three phases, so that output row a = 0 is complete (and drains) before the
+// last phase and a = 1 drains under the next unit's first:
+//   phase A  row i = 0            slots of 32 input channels: four [128 x 32] A tiles + four [64 x 32] weight tiles
+//   phase B  rows i = 1 and 2     slots of 16 input channels: eight [128 x 16] A tiles + eight [64 x 16] weight tiles;
+//                                 both rows are built from the same two input rows (d1 + d2 and d2 - d1), which
+//                                 therefore travel to shared memory and to the registers once for the two of them
+//   phase C  row i = 3            as phase A
+// Every slot is one A group of 128 tensor-memory columns and 32 KB of weights, and carries 48 MMAs (24 in the
+// phases where only one output row takes part).  A step is one team's half of a slot:
 //   * the X producer (warp 4) brings, by TMA, the input rows a step needs into a ring of shared-memory
-//     buffers: rows d1,d2 of every tile for i = 1, 2 (a dense box), rows d0,d2 (i = 0) or d1,d3 (i = 3) through
-//     a tensor map that walks the image with a row stride of 2, so only the rows that are used travel;
-//     out-of-image rows, columns and channels arrive as zeros, which is the layer's padding;
+//     buffers: rows d0,d2 (phase A) or d1,d3 (phase C) of 16 channels through a tensor map that walks the image
+//     with a row stride of 2, rows d1,d2 of 8 channels as a dense box in phase B; out-of-image rows, columns and
+//     channels arrive as zeros, which is the layer's padding;
 //   * two teams of eight transform warps fill the two halves of every slot side by side; a thread owns one
-//     tile x 8 channels: two 8-byte loads per channel give the middle pixels of its window, the outer two come
-//     from the neighbouring lanes by shuffle; an optional per-channel affine map (a BatchNorm in front of the
-//     layer) is applied on the fly without touching the zero padding;
-//   * the W producer (warp 6) streams the slot's four weight tiles (B operands);
-//   * four MMA issuers (warps 0..3, one thread each), one per output accumulator (a, e): a single issuing
-//     thread gets too few issue slots next to the transform warps to keep the tensor core fed, and each
-//     accumulator has one owner.  (Roles must not share a warp: a lane that waits on an mbarrier stalls the
-//     other lanes of its warp too.)
-//   * the eight epilogue warps read output row a = 0 as soon as Winograd row 2 is done (row 3 does not touch
-//     it) and row a = 1 after row 3, stage 16 channels at a time in shared memory (optional per-channel
-//     affine) and hand the box to a TMA store (row stride 2 in Y), which also clips odd sizes and partial
-//     blocks -- or to a TMA reduce-add when Y already holds a shortcut to add to.
-// Tensor memory: columns 0..255 = the accumulators (a, e) at (2a + e) * 64, 256..511 = a ring of two A groups
-// (4 tiles x 32 columns each).  A unit is NB images x TH tile rows x TW tile columns (at most 128 tiles, one
-// TMEM lane each; a tile row takes a power-of-two number of lanes) x 64 output channels.  Each input row is
-// fetched once per Winograd row that uses it (from L2 after the first time); HBM sees X once and Y once.
+//     tile: two 8-byte loads per channel give the middle pixels of its window, the outer two come from the
+//     neighbouring lanes by shuffle; an optional per-channel affine map (a BatchNorm in front of the layer) is
+//     applied on the fly without touching the zero padding;
+//   * the W producer (warp 6) streams the slot's weight tiles (B operands);
+//   * four MMA issuers (warps 0..3), one per output accumulator (a, e): each walks its loop as a whole warp with
+//     warp-uniform operands and lets one elected lane issue (a lone lane issuing from per-thread registers takes
+//     several times as many issue slots, for which the transform warps compete);
+//   * the eight epilogue warps read output row a = 0 as soon as phase B is done and row a = 1 after phase C, stage
+//     16 channels at a time in one of two shared-memory boxes (optional per-channel affine) and hand the box to a
+//     TMA store (row stride 2 in Y), which also clips odd sizes and partial blocks -- or to a TMA reduce-add when
+//     Y already holds a shortcut to add to.
+// Tensor memory: columns 0..255 = the accumulators (a, e) at (2a + e) * 64, 256..511 = a ring of two A groups.
+// A unit is NB images x TH tile rows x TW tile columns (at most 128 tiles, one TMEM lane each; a tile row takes
+// a power-of-two number of lanes) x 64 output channels.  HBM sees X once and Y once.
 // Every waiter sees every phase of a barrier it waits on (a parity wait cannot tell a phase from the one two
 // before it); all waits are bounded and end in a status word instead of a hang.
 #pragma once
 #include <type_traits>
 
 constexpr int kFuAGroups = 2;                      // ring of A groups in tensor memory; a group = four [128 x 32] tiles
-constexpr int kFuGroupCols = 4 * 32;               // tensor-memory columns of an A group
+constexpr int kFuGroupCols = 4 * 32;               // tensor-memory columns of an A group (phase B: 8 tiles x 16)
 constexpr int kFuACol0 = 4 * kBlockN;              // first tensor-memory column of the A ring
 constexpr int kFuWStages = kFuAGroups;            // a W stage travels with its A group: one "slot" of the ring
 constexpr int kFuWTile = 64 * 128;                 // one [64 out-channels][32 channels] tile, rows of 128 bytes
 constexpr int kFuWBytes = 4 * kFuWTile;            // four of them, one per Winograd column j
-constexpr int kFuXbufs = 4;
+#ifndef WG_FU_XBUFS
+#define WG_FU_XBUFS 5
+#endif
+#ifndef WG_FU_YBOXES
+#define WG_FU_YBOXES 1
+#endif
+constexpr int kFuXbufs = WG_FU_XBUFS;
 constexpr int kFuXfull = 2 * kFuXbufs;             // full-barriers of the X ring (see the kernel)
-constexpr int kFuXbufBytes = 32768;
+constexpr int kFuXbufBytes = 24576;                // the larger box: (TH + 1) rows x BW x 16 channels x NB images
+constexpr int kFuYBoxes = WG_FU_YBOXES;            // staging boxes of Y per epilogue warpgroup
 constexpr int kFuTeamWarps = 8;                    // transform warps per team: one thread = one tile x 8 channels
 constexpr int kFuThreads = 256 + 256 + 2 * 32 * kFuTeamWarps;   // 2 control WGs, 2 epilogue WGs, 2 transform teams (2 WGs each)
-constexpr int kFuYStageBytes = kFuXbufBytes / 2;  // per epilogue warpgroup: one [NB][16 channels][TH rows][2*TW pixels] box of Y
-                                                   // (a fourth X buffer is worth more than a second box: 50.9 vs 53.8 us)
-constexpr int kFuSmemBytes = kFuWStages * kFuWBytes + kFuXbufs * kFuXbufBytes + 2 * kFuYStageBytes + kCtrlBytes + 1024;
+constexpr int kFuYStageBytes = 16384;              // one [NB][16 channels][TH rows][2*TW pixels] box of Y
+constexpr int kFuW2Tile = 64 * 64;                 // phase B: one [64 out-channels][16 channels] tile, rows of 64 bytes
+constexpr int kFuSmemBytes = kFuWStages * kFuWBytes + kFuXbufs * kFuXbufBytes + 2 * kFuYBoxes * kFuYStageBytes + kCtrlBytes + 1024;
 static_assert(kFuACol0 + kFuAGroups * kFuGroupCols <= (int)kTmemCols, "tensor memory columns");
 static_assert(kFuSmemBytes <= 232448, "shared memory per CTA");
 // Register hand-over (setmaxnreg): the kernel starts with 64 registers per thread; the increase of the transform
@@ -78,7 +90,7 @@ struct FuParams {
     int lp_log2;                     // a tile row takes 2^lp_log2 >= TW TMEM lanes
     int nRB, nSeg, nGroups, nKB, nC32;        // nC32 = ring slots (32 input channels each) per Winograd row
     int units, relu;
-    uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows) and of the row-stride-2 (TH+1 rows) box
+    uint32_t xbytes1, xbytes2;       // bytes of the dense (2*TH rows, 8 channels) and of the row-stride-2 (TH+1 rows, 16 channels) box
     uint32_t spin_limit;             // polls before a wait gives up (wg2x2_set_wait_limit)
     int drop_load;                   // >= 0: the W producer of CTA 0 leaves out its drop_load-th slot (wg2x2_test_drop_load), else -1
 };
@@ -189,8 +201,9 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 
 template <bool EXTRAS, bool AFFINE>
 __global__ void __launch_bounds__(kFuThreads, 1)
-layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_constant__ CUtensorMap mapX2,
-                       const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapY, const FuParams prm)
+layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapXd, const __grid_constant__ CUtensorMap mapXs,
+                       const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapW2,
+                       const __grid_constant__ CUtensorMap mapY, const FuParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -199,13 +212,13 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     constexpr int kWOff = 0;
     constexpr int kXOff = kWOff + kFuWStages * kFuWBytes;
     constexpr int kYOff = kXOff + kFuXbufs * kFuXbufBytes;
-    constexpr int kBarOff = kYOff + 2 * kFuYStageBytes;
+    constexpr int kBarOff = kYOff + 2 * kFuYBoxes * kFuYStageBytes;
     const uint32_t wbase = base + kWOff, xbase = base + kXOff, bars = base + kBarOff;
     const float *xgen = reinterpret_cast<const float *>(gen_base + kXOff);
     uint64_t *bars_gen = reinterpret_cast<uint64_t *>(gen_base + kBarOff);
     // barriers: full[G] (both halves of the A group written, one by each team, and the W tiles landed), free[G] (the four issuers' MMAs on the
     // slot are complete), acc_full[2] / acc_empty[2] (per output row a), xfull[2*XB], xempty[XB], ywritten[2], yfree[2].
-    // A step is 16 input channels; steps 2s and 2s+1 (one per team) fill the two halves of 32-channel slot s.
+    // Steps 2s and 2s+1 (one per team) fill the two halves of slot s.
     // Step n fills X buffer n % XB but signals xfull[n % (2*XB)]: with an odd XB the two teams take turns on a
     // buffer, and a parity wait can only tell a barrier's current phase from the one before it, so a waiter has
     // to see every phase of the barrier it waits on; xfull[j] is always the same team's.
@@ -222,8 +235,6 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     auto yfree_bar = [&](int h) { return bars + 8u * (kB7b + 2 + h); };
     volatile uint32_t *tmem_ptr_slot = reinterpret_cast<volatile uint32_t *>(bars_gen + kB8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(bars_gen + kB8 + 1);
-    volatile int *team_ok = reinterpret_cast<volatile int *>(bars_gen + kB8 + 2);   // [2]: verdict of a team's polling warp
-    (void)team_ok;
 
     // (broadcast from lane 0: the compiler then treats the warp index, and all that is derived from it, as warp-uniform)
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -255,6 +266,8 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int nC32 = prm.nC32;
+    // per unit: slots 0 .. nC32-1 are phase A, nC32 .. 3*nC32-1 phase B, 3*nC32 .. 4*nC32-1 phase C; two steps per slot
+    const int spu_slots = 4 * nC32;
     auto decode = [&](int u, int &g, int &rb, int &seg, int &kb) {
         kb = u % prm.nKB; u /= prm.nKB;
         seg = u % prm.nSeg; u /= prm.nSeg;
@@ -269,22 +282,24 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             // ------------------------------ MMA issuers -----------------------------------
             // Issuer (a, e) = warp (2a + e) owns that accumulator: position (i, j) goes into it with the sign
             // At[a][i] * At[e][j]; At = [[1,1,1,0],[0,1,-1,-1]], so column e takes j = e..e+2 and row a takes
-            // i = a..a+2.  On the one row it has nothing to add the issuer still follows the ring (wait, commit).
-            // The whole warp walks the loop with warp-uniform values (warp index and tensor-memory base were
-            // broadcast from lane 0), so that descriptors and addresses live in uniform registers; one elected lane
-            // issues the MMAs and the commits.
+            // i = a..a+2: a = 0 is idle in phase C and a = 1 in phase A, where the issuer still follows the ring
+            // (wait, arrive).  The whole warp walks the loop with warp-uniform values (warp index and tensor-memory
+            // base were broadcast from lane 0), so that descriptors and addresses live in uniform registers; one
+            // elected lane issues the MMAs and the commits.
             constexpr uint32_t idesc_pos = make_idesc_tf32(kBlockM, kBlockN);
             constexpr uint32_t idesc_neg = idesc_pos | (1u << 14);            // negate B
             const bool leader = elect_one();
             const int a = warp >> 1, e = warp & 1;
             const uint32_t d_tmem = tmem_base + (uint32_t)(warp * kBlockN);
-            const uint32_t a_tmem0 = tmem_base + (uint32_t)(kFuACol0 + e * 32);
-            const uint64_t bdesc0 = make_desc_k_sw128(wbase + e * kFuWTile);
+            const uint32_t a_tmem0 = tmem_base + (uint32_t)kFuACol0;
+            const uint64_t bdesc0 = make_desc_k_sw128(wbase), b2desc0 = make_desc_k_sw64(wbase);
             const uint32_t b_hi = (uint32_t)(bdesc0 >> 32), b_lo0 = (uint32_t)bdesc0;
+            const uint32_t b2_hi = (uint32_t)(b2desc0 >> 32), b2_lo0 = (uint32_t)b2desc0;
             const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-            const int total = my_units * 4 * nC32;
+            const int total = my_units * spu_slots;
+            const int first_slot = a == 0 ? 0 : nC32, last_slot = a == 0 ? 3 * nC32 - 1 : 4 * nC32 - 1;   // of this accumulator, in a unit
             int g = 0; uint32_t gph = 0;
-            int i = 0, cc = 0;
+            int sl = 0;                                                       // slot within the unit
             uint32_t units_done = 0;
             int trm = 0; (void)trm;
             // this issuer's copy of the unit's sixteen zero-block words (bit cc: the [64 x 32] weight tile of position t,
@@ -293,10 +308,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const uint32_t *my_masks32 = reinterpret_cast<const uint32_t *>(my_masks);
             bool dense = true;
             for (int n = 0; n < total; ++n) {
-                if (cc == 0 && i == 0) {
+                if (sl == 0) {
                     int gu, rbu, segu, kbu;
                     decode((int)blockIdx.x + (int)units_done * (int)gridDim.x, gu, rbu, segu, kbu);
                     unsigned long long all = ~0ull;
+                    __syncwarp();
                     if (lane < 16) {
                         all = __ldg(prm.masks + (long long)lane * prm.nKB + kbu);
                         my_masks[lane] = all;
@@ -307,26 +323,49 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm);
                 if (!mbar_wait_warp(full_bar(g), gph, abort_flag, 0x1000u | (warp << 8) | g, prm.spin_limit)) break;
                 if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm + 1);
-                // the row's first MMA overwrites the accumulator: the epilogue must have read the previous unit's
-                if (cc == 0 && i == a && !mbar_wait_warp(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a, prm.spin_limit)) break;
+                // this accumulator's first MMA of the unit overwrites it: the epilogue must have read the previous unit's
+                if (sl == first_slot && !mbar_wait_warp(acce_bar(a), (units_done & 1u) ^ 1u, abort_flag, 0x1400u | (warp << 8) | a, prm.spin_limit)) break;
                 if (warp == 0 && leader) TC_TRACE(1024 + 5 * trm + 2);
                 tc_fence_after();
-                int g2 = g + 1; uint32_t gph2 = gph;
-                if (g2 == kFuAGroups) { g2 = 0; gph2 ^= 1u; }
-                const bool active = i >= a && i <= a + 2;
-                if (active) {
-                    const bool neg_a = (a == 1 && i >= 2);
-                    const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols), b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
+                const int phase = sl < nC32 ? 0 : (sl < 3 * nC32 ? 1 : 2);
+                const bool active = phase == 1 || phase == 2 * a;
+                const uint32_t a_tmem = a_tmem0 + (uint32_t)(g * kFuGroupCols);
+                if (active && phase != 1) {
+                    // one Winograd row, 32 channels: tile j at columns j*32, its two 16-channel halves 16 columns apart
+                    const int i = phase == 0 ? 0 : 3, cc = phase == 0 ? sl : sl - 3 * nC32;
+                    const bool neg_a = phase == 2;                                    // At[1][3] = -1, At[0][0] = +1
+                    const uint32_t b_lo = b_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
 #pragma unroll
                     for (int jj = 0; jj < 3; ++jj) {
-                        // an all-zero weight tile adds nothing (the slot's first chunk always runs: it zero-initialises)
+                        // an all-zero weight tile adds nothing (the unit's first chunk always runs: it zero-initialises)
                         if (!dense && cc > 0 && cc < 64 && !((my_masks32[2 * (4 * i + e + jj) + (cc >> 5)] >> (cc & 31)) & 1u)) continue;
                         const bool neg_e = (e == 1 && jj >= 1);                      // At[1][j] = -1 for j = 2, 3
                         const uint32_t idesc = (neg_a != neg_e) ? idesc_neg : idesc_pos;
-                        const uint32_t aj = a_tmem + (uint32_t)(jj * 32), bj = b_lo + (uint32_t)(jj * (kFuWTile >> 4));
+                        const uint32_t aj = a_tmem + (uint32_t)((e + jj) * 32), bj = b_lo + (uint32_t)((e + jj) * (kFuWTile >> 4));
+#ifndef WG_KO_MMA  // (development knock-out: no MMAs, results wrong)
                         if (leader) {
-                            umma_tf32_ts_x2(d_tmem, aj, bj, b_hi, idesc, (jj == 0 && cc == 0 && i == a) ? 0u : 1u);
+                            umma_tf32_ts_x2(d_tmem, aj, bj, b_hi, idesc, (jj == 0 && sl == first_slot) ? 0u : 1u);
                             umma_tf32_ts_x2(d_tmem, aj + 16u, bj + 4u, b_hi, idesc, 1u);
+                        }
+#endif
+                    }
+                } else if (active) {
+                    // Winograd rows 1 and 2, 16 channels: tile (i - 1) * 4 + j at columns 16 * tile, weights in rows of 64 bytes
+                    const int c16 = sl - nC32, cc = c16 >> 1;
+                    const uint32_t b_lo = b2_lo0 + (uint32_t)(g * (kFuWBytes >> 4));
+#pragma unroll
+                    for (int ii = 1; ii <= 2; ++ii) {
+                        const bool neg_a = (a == 1 && ii == 2);                          // At[1][2] = -1
+#pragma unroll
+                        for (int jj = 0; jj < 3; ++jj) {
+                            if (!dense && cc > 0 && cc < 64 && !((my_masks32[2 * (4 * ii + e + jj) + (cc >> 5)] >> (cc & 31)) & 1u)) continue;
+                            const bool neg_e = (e == 1 && jj >= 1);
+                            const uint32_t idesc = (neg_a != neg_e) ? idesc_neg : idesc_pos;
+                            const int tile = (ii - 1) * 4 + e + jj;
+                            const uint32_t aj = a_tmem + (uint32_t)(tile * 16), bj = b_lo + (uint32_t)(tile * (kFuW2Tile >> 4));
+#ifndef WG_KO_MMA
+                            if (leader) umma_tf32_ts_x2(d_tmem, aj, bj, b2_hi, idesc, (ii == 1 && jj == 0 && sl == first_slot) ? 0u : 1u);
+#endif
                         }
                     }
                 }
@@ -334,35 +373,40 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 if (leader) {
                     // (an issuer that added nothing in this slot has nothing for a commit to track: it arrives directly)
                     if (active) umma_commit(free_bar(g)); else mbar_arrive(free_bar(g));
-                    if (cc == nC32 - 1 && i == a + 2) umma_commit(accf_bar(a));          // this accumulator is complete
+                    if (sl == last_slot) umma_commit(accf_bar(a));                   // this accumulator is complete
                 }
                 __syncwarp();
                 if (warp == 0 && leader) { TC_TRACE(1024 + 5 * trm + 4); ++trm; }
-                g = g2; gph = gph2;
-                if (++cc == nC32) { cc = 0; if (++i == 4) { i = 0; ++units_done; } }
+                if (++g == kFuAGroups) { g = 0; gph ^= 1u; }
+                if (++sl == spu_slots) { sl = 0; ++units_done; }
             }
         } else if (warp == 4 && lane == 0) {
             // ------------------------------ X producer -----------------------------------
-            int xb = 0, xj = 0; uint32_t xph = 0;               // buffer n % XB (xempty phase parity xph), barrier xfull[n % (4*XB)]
+            int xb = 0, xj = 0; uint32_t xph = 0;               // buffer n % XB (xempty phase parity xph), barrier xfull[n % (2*XB)]
             bool ok = true;
             int trx = 0; (void)trx;
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 int g, rb, seg, kb;
                 decode(u, g, rb, seg, kb);
                 const int x0 = 2 * seg * prm.TW - 4, th0 = rb * prm.TH, b0 = g * prm.NB;
-                for (int i = 0; i < 4 && ok; ++i) {
-                    const bool strided = (i == 0 || i == 3);
-                    const int h_lo = 2 * th0 - (i == 0 ? 1 : 0);
-                    const CUtensorMap *map = strided ? &mapX2 : &mapX1;
-                    const uint32_t bytes = strided ? prm.xbytes2 : prm.xbytes1;
-                    for (int cc = 0; cc < 2 * nC32; ++cc) {     // channels beyond C arrive as zeros
-                        if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100, prm.spin_limit)) { ok = false; break; }
-                        TC_TRACE(trx); ++trx;
-                        mbar_expect_tx(xfull_bar(xj), bytes);
-                        tma_load_4d(xbase + xb * kFuXbufBytes, map, xfull_bar(xj), x0, h_lo, cc * 16, b0);
-                        if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
-                        if (++xj == kFuXfull) xj = 0;
+                for (int st = 0; st < 2 * spu_slots; ++st) {       // channels beyond C arrive as zeros
+                    if (!mbar_wait_sleepy(xempty_bar(xb), xph ^ 1u, abort_flag, 0x900u | xb, 100, prm.spin_limit)) { ok = false; break; }
+                    TC_TRACE(trx); ++trx;
+                    const uint32_t dst = xbase + xb * kFuXbufBytes;
+#ifdef WG_KO_X     // development knock-out: no input loads (results wrong)
+                    mbar_arrive(xfull_bar(xj)); (void)dst; (void)x0; (void)th0; (void)b0;
+#else
+                    if (st >= 2 * nC32 && st < 6 * nC32) {         // phase B: rows d1, d2 of 8 channels, dense
+                        mbar_expect_tx(xfull_bar(xj), prm.xbytes1);
+                        tma_load_4d(dst, &mapXd, xfull_bar(xj), x0, 2 * th0, (st - 2 * nC32) * 8, b0);
+                    } else {                                       // phase A: rows d0, d2; phase C: rows d1, d3 (every second row)
+                        const bool first = st < 2 * nC32;
+                        mbar_expect_tx(xfull_bar(xj), prm.xbytes2);
+                        tma_load_4d(dst, &mapXs, xfull_bar(xj), x0, 2 * th0 - (first ? 1 : 0), (first ? st : st - 6 * nC32) * 16, b0);
                     }
+#endif
+                    if (++xb == kFuXbufs) { xb = 0; xph ^= 1u; }
+                    if (++xj == kFuXfull) xj = 0;
                 }
             }
             if (!ok)
@@ -375,15 +419,20 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
                 int g, rb, seg, kb;
                 decode(u, g, rb, seg, kb);
-                for (int i = 0; i < 4 && ok; ++i)
-                    for (int cc = 0; cc < nC32; ++cc) {
-                        if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100, prm.spin_limit)) { ok = false; break; }
-                        // test hook: this slot's weights never arrive (nothing is put in flight), so the issuers' wait on it runs out
-                        if (blockIdx.x == 0 && nload++ == prm.drop_load) { ok = false; break; }
-                        mbar_expect_tx(full_bar(s), kFuWBytes);
-                        tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), cc * 32, kb * kBlockN, 4 * i);
-                        if (++s == kFuWStages) { s = 0; ph ^= 1u; }
-                    }
+                for (int sl = 0; sl < spu_slots; ++sl) {
+                    if (!mbar_wait_sleepy(free_bar(s), ph ^ 1u, abort_flag, 0xA00u | s, 100, prm.spin_limit)) { ok = false; break; }
+                    // test hook: this slot's weights never arrive (nothing is put in flight), so the issuers' wait on it runs out
+                    if (blockIdx.x == 0 && nload++ == prm.drop_load) { ok = false; break; }
+#ifdef WG_KO_W     // development knock-out: no weight loads (results wrong)
+                    mbar_arrive(full_bar(s));
+#else
+                    mbar_expect_tx(full_bar(s), kFuWBytes);
+                    if (sl < nC32)          tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), sl * 32, kb * kBlockN, 0);
+                    else if (sl < 3 * nC32) tma_load_3d(wbase + s * kFuWBytes, &mapW2, full_bar(s), (sl - nC32) * 16, kb * kBlockN, 4);
+                    else                    tma_load_3d(wbase + s * kFuWBytes, &mapW, full_bar(s), (sl - 3 * nC32) * 32, kb * kBlockN, 12);
+#endif
+                    if (++s == kFuWStages) { s = 0; ph ^= 1u; }
+                }
             }
             if (!ok)
                 for (int it = 0; it < 1000; ++it) __nanosleep(1000);
@@ -394,7 +443,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int team = (warp - 16) / kFuTeamWarps;
         const int tw8 = (warp - 16) % kFuTeamWarps;
         const int l = (tw8 & 3) * 32 + lane;                   // tile = TMEM lane = A-tile row
-        const int hq = tw8 >> 2;                               // which 8 of the step's 16 channels
+        const int hq = tw8 >> 2;                               // which half of the step's channels
         // a tile row occupies LP = 2^lp_log2 >= TW consecutive lanes, so it never straddles a warp (or, for
         // LP <= 16, a half-warp: the 8-byte loads of a half-warp then stay conflict-free)
         const int trow = l >> prm.lp_log2, tcol = l & ((1 << prm.lp_log2) - 1);
@@ -413,26 +462,24 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int src_l = (lane & ~(LP - 1)) | ((tcol + LP - 1) & (LP - 1)), src_r = (lane & ~(LP - 1)) | ((tcol + 1) & (LP - 1));
         const bool need_l = !halo_by_lanes && (tcol == 0), need_r = !halo_by_lanes && ((tcol == prm.TW - 1) || (tcol == LP - 1));
         const float lo = prm.relu ? 0.f : -__int_as_float(0x7f800000);
-        const int spu = 8 * nC32;                               // 16-channel steps per unit: 4 Winograd rows x 2 per slot
+        const int spu = 2 * spu_slots;                          // steps per unit
         const int my_units = (prm.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total = my_units * spu;
-        // Step n = 16 input channels of one Winograd row; steps 2s and 2s+1 fill the two halves of ring slot s
-        // (A group s % 2).  This team takes the steps n = 2k + team, i.e. its own half of every slot, so the two
-        // teams work on a slot side by side and both see every phase of the slot's barriers.
-        // X buffer n % kFuXbufs, full-barrier n % kFuXfull.
+        // Steps 2s and 2s+1 fill the two halves of ring slot s (A group s % 2).  This team takes the steps
+        // n = 2k + team, i.e. its own half of every slot, so the two teams work on a slot side by side and both
+        // see every phase of the slot's barriers.  X buffer n % kFuXbufs, full-barrier n % kFuXfull.
         static_assert(kFuAGroups == 2 && kFuXfull % 2 == 0, "each xfull barrier belongs to one team");
-        const int half = team;                                 // which 16 of a slot's 32 channels
         bool ok = true;
         int trt = 0; (void)trt;
-        // running values of n % kFuXfull (and its wrap parity), of the Winograd row and of the slot within the row
-        int xj = team, i = 0, c32 = 0;
+        // running values of n % kFuXfull (and its wrap parity) and of the step within the unit
+        int xj = team, st = team;
         uint32_t xph = 0;
         // AFFINE: the image is s_c * x + t_c inside and 0 in the padding, so B^T d B = s_c * (B^T x B) + t_c * R_i * C_j
         // with R = B^T rowmask, C = B^T colmask of the tile's 4 x 4 window (R = C = (0,2,0,0) away from the border)
         int unit = blockIdx.x;
         float Rm[4] = {0.f, 0.f, 0.f, 0.f}, Cm[4] = {0.f, 0.f, 0.f, 0.f};
         for (int k = 0, n = team; n < total; ++k, n += 2) {
-            if (AFFINE && i == 0 && c32 == 0) {
+            if (AFFINE && st == team) {
                 int gu, rbu, segu, kbu;
                 decode(unit, gu, rbu, segu, kbu);
                 unit += gridDim.x;
@@ -449,119 +496,164 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
             const int g = k & 1;
             const uint32_t gph = (uint32_t)(k >> 1) & 1u;          // slot k is this group's (k / 2)-th filling
             const int xb = xj < kFuXbufs ? xj : xj - kFuXbufs;
-            const bool strided = (i == 0 || i == 3);
-            const int rows = strided ? prm.TH + 1 : 2 * prm.TH;
-            const int ra = strided ? thl : 2 * thl + (i == 2 ? 1 : 0);
-            const int dab = (i == 2 ? -1 : 1) * BW;              // from row a to row b
-            const float sb = (i == 1) ? 1.f : -1.f;              // row i of B^T d = a + sb * b
-            // AFFINE: the shift term of this step is t_c * R_i * C_j
-            const float Ri = AFFINE ? (i == 0 ? Rm[0] : i == 1 ? Rm[1] : i == 2 ? Rm[2] : Rm[3]) : 0.f;
-            const float RC0 = Ri * Cm[0], RC1 = Ri * Cm[1], RC2 = Ri * Cm[2], RC3 = Ri * Cm[3];
-            // AFFINE: this thread's 8 channels' scale and shift, fetched before the waits so that their latency hides there
+            const int phase = st < 2 * nC32 ? 0 : (st < 6 * nC32 ? 1 : 2);
+            const bool mid = phase == 1;                         // rows 1 and 2 together, from input rows d1 and d2
+            // first channel of the step and the thread's first channel within it (8 per thread, 4 in phase B)
+            const int ch_step = mid ? (st - 2 * nC32) * 8 : (phase == 0 ? st : st - 6 * nC32) * 16;
+            const int ch_mine = mid ? 4 * hq : 8 * hq;
+            const int rows = mid ? 2 * prm.TH : prm.TH + 1;      // rows of a channel in the X buffer
+            const int nch = mid ? 8 : 16;                        // channels of an image in the X buffer
+            const int ra = mid ? 2 * thl : thl;                  // first of the tile's two input rows; the second is the next one
+            const float sb = phase == 0 ? -1.f : (phase == 2 ? -1.f : 1.f);   // phase A: d0 - d2; phase C: d1 - d3
+            // AFFINE: the shift term of a value is t_c * R_i * C_j
+            float RCa[4], RCb[4];                                // row i = 0 / 3 (or 1 in phase B), and row 2 in phase B
+            if (AFFINE) {
+                const float Ri = phase == 0 ? Rm[0] : (phase == 2 ? Rm[3] : Rm[1]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { RCa[j] = Ri * Cm[j]; RCb[j] = Rm[2] * Cm[j]; }
+            }
+            // AFFINE: this thread's channels' scale and shift, fetched before the waits so that their latency hides there
             float sc8[8], tc8[8];
             if (AFFINE) {
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const int chg = c32 * 32 + half * 16 + hq * 8 + c;
-                    sc8[c] = chg < prm.C ? __ldg(prm.in_scale + chg) : 0.f;
-                    tc8[c] = chg < prm.C ? __ldg(prm.in_shift + chg) : 0.f;
+                    const int chg = ch_step + ch_mine + c;
+                    const bool in = chg < prm.C && (c < 4 || !mid);
+                    sc8[c] = in ? __ldg(prm.in_scale + chg) : 0.f;
+                    tc8[c] = in ? __ldg(prm.in_shift + chg) : 0.f;
                 }
             }
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt);
             // both waits, then one vote (the warp converged and of one mind before the aligned instructions below)
-#if defined(WG_FU_TEAM_POLL)
-            // one warp of the team polls the two barriers; the other seven wait for it at a named barrier, where they
-            // take no issue slots from the warps that have work
-            bool got_a = true;
-            if (tw8 == 0) {
-                const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, prm.spin_limit);
-                got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, prm.spin_limit);
-                got_a = __all_sync(0xffffffffu, got_a);
-                if (lane == 0) team_ok[team] = got_a ? 1 : 0;
-            }
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + team), "n"(32 * kFuTeamWarps) : "memory");
-            got_a = team_ok[team] != 0;
-            if (!got_a) { ok = false; break; }
-#elif defined(WG_FU_XF_SLEEP)
-            const bool got_x = mbar_wait_sleepy(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, WG_FU_XF_SLEEP, prm.spin_limit);
-            if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
-            const bool got_a = got_x && mbar_wait_sleepy(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, WG_FU_XF_SLEEP, prm.spin_limit);
-            if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
-#else
             const bool got_x = mbar_wait(xfull_bar(xj), xph, abort_flag, 0xB00u | xj, prm.spin_limit);
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 1);
             const bool got_a = got_x && mbar_wait(free_bar(g), gph ^ 1u, abort_flag, 0xC00u | g, prm.spin_limit);
             if (!__all_sync(0xffffffffu, got_a)) { ok = false; break; }
-#endif
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 2);
             const int chs = rows * BW;
-            const float *xq = xgen + xb * (kFuXbufBytes / 4) + (bi * 16 * rows + ra) * BW + 2 * twl + 3;
-            const uint32_t xq_s = xbase + (uint32_t)(xb * kFuXbufBytes + 4 * ((bi * 16 * rows + ra) * BW + 2 * twl + 4));   // the 8-byte loads, shared-space address
+            const int off0 = ((bi * nch + ch_mine) * rows + ra) * BW + 2 * twl;
+            const float *xq = xgen + xb * (kFuXbufBytes / 4) + off0 + 3;
+            const uint32_t xq_s = xbase + (uint32_t)(xb * kFuXbufBytes + 4 * (off0 + 4));   // the 8-byte loads, shared-space address
             tc_fence_after();
-            const uint32_t a_tmem = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * kFuGroupCols + half * 16);
-            // (two copies of the loop, so that the common case carries no test for the lanes at the ends of a tile row)
-            auto quads = [&](auto by_lanes_tag) {
-            constexpr bool kByLanes = decltype(by_lanes_tag)::value;
+            const uint32_t a_grp = tmem_base + ((uint32_t)((tw8 & 3) * 32) << 16) + (uint32_t)(kFuACol0 + g * kFuGroupCols);
+            // the row combination a + sb * b of the tile's four window pixels: the middle two from one 8-byte load per
+            // input row, the outer two from the neighbouring lanes
+            auto window = [&](auto by_lanes_tag, int c, float s2, float &r0, float &r1, float &r2, float &r3) {
+                constexpr bool kByLanes = decltype(by_lanes_tag)::value;
+                const float *pa = xq + c * chs;
+                const float *pb = pa + BW;
+#ifdef WG_KO_LDS   // development knock-out: no shared-memory loads (results wrong)
+                const float2 am = make_float2((float)c, s2), bm = make_float2(s2, 1.f);
+#else
+                const float2 am = lds_f2(xq_s + (uint32_t)(4 * c * chs));
+                const float2 bm = lds_f2(xq_s + (uint32_t)(4 * (c * chs + BW)));
+#endif
+                r1 = fmaf(s2, bm.x, am.x); r2 = fmaf(s2, bm.y, am.y);
+#ifdef WG_KO_SHFL  // development knock-out: no shuffles (results wrong)
+                r0 = r2 * 0.5f; r3 = r1 * 0.25f;
+#else
+                r0 = __shfl_sync(0xffffffffu, r2, src_l); r3 = __shfl_sync(0xffffffffu, r1, src_r);
+#endif
+                if (!kByLanes) {
+                    if (need_l) r0 = fmaf(s2, pb[0], pa[0]);
+                    if (need_r) r3 = fmaf(s2, pb[3], pa[3]);
+                }
+            };
+            auto body = [&](auto by_lanes_tag) {
+                if (!mid) {
+                    // one Winograd row of 16 channels: this thread's 8 channels as two quads, tile j at columns j*32
+                    const uint32_t a_tmem = a_grp + (uint32_t)(team * 16);
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int c4 = 2 * hq + q;
-                float o[4][4];   // [j][channel within the quad]
+                    for (int q = 0; q < 2; ++q) {
+                        const int c4 = 2 * hq + q;
+                        float o[4][4];   // [j][channel within the quad]
 #pragma unroll
-                for (int cq = 0; cq < 4; ++cq) {
-                    // row i of B^T d at the tile's 4 pixels: the middle two from one 8-byte load per input row, the outer
-                    // two from the neighbouring lanes
-                    const float *pa = xq + (c4 * 4 + cq) * chs;
-                    const float *pb = pa + dab;
-#ifdef WG_TC_BOUNDS   // development build: bounds of the two 8-byte loads, recorded instead of faulting
-                    {
-                        const long long oa = (pa + 1) - xgen, ob = (pb + 1) - xgen;
-                        if (oa < 0 || ob < 0 || oa + 1 >= kFuXbufs * (kFuXbufBytes / 4) || ob + 1 >= kFuXbufs * (kFuXbufBytes / 4) || (oa & 1) || (ob & 1)) {
-                            g_tc_status[1] = 0xEE000000u | (unsigned)(oa & 0xFFFFFF);
-                            g_tc_status[0] = 2;
-                            continue;
+                        for (int cq = 0; cq < 4; ++cq) {
+                            float r0, r1, r2, r3;
+                            window(by_lanes_tag, q * 4 + cq, sb, r0, r1, r2, r3);
+                            // (fp32 values; what the tensor core makes of the low mantissa bits: see tmem_st4)
+                            if (AFFINE) {
+                                const float sc = sc8[q * 4 + cq], tc = tc8[q * 4 + cq];
+                                o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * RCa[0]), lo);
+                                o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tc * RCa[1]), lo);
+                                o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tc * RCa[2]), lo);
+                                o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tc * RCa[3]), lo);
+                            } else {
+                                o[0][cq] = fmaxf(r0 - r2, lo);
+                                o[1][cq] = fmaxf(r1 + r2, lo);
+                                o[2][cq] = fmaxf(r2 - r1, lo);
+                                o[3][cq] = fmaxf(r1 - r3, lo);
+                            }
+                        }
+#ifdef WG_KO_ST    // development knock-out: one tensor-memory store instead of four (results wrong)
+                        { float z[4] = {o[0][0] + o[1][1], o[2][2] + o[3][3], o[0][1] + o[1][2], o[2][3] + o[3][0]}; tmem_st4(a_tmem + (uint32_t)(c4 * 4), z); }
+#else
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
+#endif
+                        if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
+                    }
+                } else {
+                    // Winograd rows 1 and 2 of 8 channels: this thread's 4 channels, tile (i - 1) * 4 + j at columns 16 * tile
+                    const uint32_t a_tmem = a_grp + (uint32_t)(team * 8 + hq * 4);
+                    // the middle pixels of both rows from one pair of loads per channel
+                    float m1[4][2], m2[4][2], e1[4][2], e2[4][2];   // [channel][left, right]: rows 1 and 2; e*: the outer pixels where lanes cannot supply them
+#pragma unroll
+                    for (int cq = 0; cq < 4; ++cq) {
+#ifdef WG_KO_LDS   // development knock-out: no shared-memory loads (results wrong)
+                        const float2 am = make_float2((float)cq, lo), bm = make_float2(lo, 1.f);
+#else
+                        const float2 am = lds_f2(xq_s + (uint32_t)(4 * cq * chs));
+                        const float2 bm = lds_f2(xq_s + (uint32_t)(4 * (cq * chs + BW)));
+#endif
+                        m1[cq][0] = am.x + bm.x; m1[cq][1] = am.y + bm.y;      // row 1 = d1 + d2
+                        m2[cq][0] = bm.x - am.x; m2[cq][1] = bm.y - am.y;      // row 2 = d2 - d1
+                        if (!decltype(by_lanes_tag)::value) {
+                            const float *pa = xq + cq * chs, *pb = pa + BW;
+                            e1[cq][0] = pa[0] + pb[0]; e1[cq][1] = pa[3] + pb[3];
+                            e2[cq][0] = pb[0] - pa[0]; e2[cq][1] = pb[3] - pa[3];
                         }
                     }
-#endif
-#ifdef WG_KO_LDS   // development knock-out: no shared-memory loads (results wrong)
-                    const float2 am = make_float2((float)cq, sb), bm = make_float2(sb, (float)q);
-#else
-                    const float2 am = lds_f2(xq_s + (uint32_t)(4 * (c4 * 4 + cq) * chs));
-                    const float2 bm = lds_f2(xq_s + (uint32_t)(4 * ((c4 * 4 + cq) * chs + dab)));
-#endif
-                    const float r1 = fmaf(sb, bm.x, am.x), r2 = fmaf(sb, bm.y, am.y);
+#pragma unroll
+                    for (int ii = 0; ii < 2; ++ii) {
+                        float o[4][4];   // [j][channel]
+#pragma unroll
+                        for (int cq = 0; cq < 4; ++cq) {
+                            const float r1 = ii == 0 ? m1[cq][0] : m2[cq][0], r2 = ii == 0 ? m1[cq][1] : m2[cq][1];
 #ifdef WG_KO_SHFL  // development knock-out: no shuffles (results wrong)
-                    float r0 = r2 * 0.5f, r3 = r1 * 0.25f;
+                            float r0 = r2 * 0.5f, r3 = r1 * 0.25f;
 #else
-                    float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
+                            float r0 = __shfl_sync(0xffffffffu, r2, src_l), r3 = __shfl_sync(0xffffffffu, r1, src_r);
 #endif
-                    if (!kByLanes) {
-                        if (need_l) r0 = fmaf(sb, pb[0], pa[0]);
-                        if (need_r) r3 = fmaf(sb, pb[3], pa[3]);
-                    }
-                    // (fp32 values; what the tensor core makes of the low mantissa bits: see tmem_st4)
-                    if (AFFINE) {
-                        const float sc = sc8[q * 4 + cq], tc = tc8[q * 4 + cq];
-                        o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * RC0), lo);
-                        o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tc * RC1), lo);
-                        o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tc * RC2), lo);
-                        o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tc * RC3), lo);
-                    } else {
-                        o[0][cq] = fmaxf(r0 - r2, lo);
-                        o[1][cq] = fmaxf(r1 + r2, lo);
-                        o[2][cq] = fmaxf(r2 - r1, lo);
-                        o[3][cq] = fmaxf(r1 - r3, lo);
+                            if (!decltype(by_lanes_tag)::value) {
+                                if (need_l) r0 = ii == 0 ? e1[cq][0] : e2[cq][0];
+                                if (need_r) r3 = ii == 0 ? e1[cq][1] : e2[cq][1];
+                            }
+                            if (AFFINE) {
+                                const float sc = sc8[cq], tc = tc8[cq];
+                                o[0][cq] = fmaxf(fmaf(sc, r0 - r2, tc * (ii == 0 ? RCa[0] : RCb[0])), lo);
+                                o[1][cq] = fmaxf(fmaf(sc, r1 + r2, tc * (ii == 0 ? RCa[1] : RCb[1])), lo);
+                                o[2][cq] = fmaxf(fmaf(sc, r2 - r1, tc * (ii == 0 ? RCa[2] : RCb[2])), lo);
+                                o[3][cq] = fmaxf(fmaf(sc, r1 - r3, tc * (ii == 0 ? RCa[3] : RCb[3])), lo);
+                            } else {
+                                o[0][cq] = fmaxf(r0 - r2, lo);
+                                o[1][cq] = fmaxf(r1 + r2, lo);
+                                o[2][cq] = fmaxf(r2 - r1, lo);
+                                o[3][cq] = fmaxf(r1 - r3, lo);
+                            }
+                        }
+#ifdef WG_KO_ST    // development knock-out: one tensor-memory store instead of four (results wrong)
+                        { float z[4] = {o[0][0] + o[1][1], o[2][2] + o[3][3], o[0][1] + o[1][2], o[2][3] + o[3][0]}; tmem_st4(a_tmem + (uint32_t)(ii * 64), z); }
+#else
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)((4 * ii + j) * 16), o[j]);
+#endif
+                        if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + ii);
                     }
                 }
-#pragma unroll
-#ifdef WG_KO_ST    // development knock-out: one tensor-memory store instead of four (results wrong)
-                { float z[4] = {o[0][0] + o[1][1], o[2][2] + o[3][3], o[0][1] + o[1][2], o[2][3] + o[3][0]}; tmem_st4(a_tmem + (uint32_t)(c4 * 4), z); }
-#else
-                for (int j = 0; j < 4; ++j) tmem_st4(a_tmem + (uint32_t)(j * 32 + c4 * 4), o[j]);
-#endif
-                if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 4 + q);
-            }
             };
-            if (halo_by_lanes) quads(std::true_type{}); else quads(std::false_type{});
+            // (two copies, so that the common case carries no test for the lanes at the ends of a tile row)
+            if (halo_by_lanes) body(std::true_type{}); else body(std::false_type{});
             // the tensor-memory writes have to be complete before the MMA issuers are told
             tmem_st_wait();
             if (warp == 16 && lane == 0) TC_TRACE(512 + 8 * trt + 6);
@@ -574,7 +666,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                 mbar_arrive(xempty_bar(xb));
             }
             xj += 2; if (xj >= kFuXfull) { xj -= kFuXfull; xph ^= 1u; }
-            if (++c32 == nC32) { c32 = 0; i = (i + 1) & 3; }
+            st += 2; if (st >= spu) st -= spu;
         }
         (void)ok;
     } else {
@@ -588,10 +680,11 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
         const int row_e = live ? trow : 0, twl = live ? tcol : 0;
         const int bi = row_e / prm.TH, thl = row_e - bi * prm.TH;
         const int BWY = prm.BWY, TH = prm.TH;
-        float *stage0 = reinterpret_cast<float *>(gen_base + kYOff + half * kFuYStageBytes);
+        float *stage0 = reinterpret_cast<float *>(gen_base + kYOff + half * kFuYBoxes * kFuYStageBytes);
         const int my_off = (bi * 16 * TH + thl) * BWY + 2 * twl; // this thread's tile in channel 0 of a box
         const bool elected = ((ew & 3) == 0) && lane == 0;
         uint32_t units_done = 0, st_use = 0;
+        int ybox = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x) {
             int g, rb, seg, kb;
@@ -617,14 +710,18 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(acce_bar(a));
                     }
-                    // the previous store of this warpgroup has left the staging area
+                    // the store that last used this staging box has left it (all but the kFuYBoxes - 1 most recent stores have been read)
                     if (elected) {
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kFuYBoxes - 1) : "memory");
                         mbar_arrive(yfree_bar(half));
                     }
                     if (!mbar_wait_warp(yfree_bar(half), st_use & 1u, abort_flag, 0x500u | ew, prm.spin_limit)) { ok = false; break; }
-                    float *stage = stage0;
+                    float *stage = stage0 + ybox * (kFuYStageBytes / 4);
+#ifdef WG_KO_Y     // development knock-out: Y is neither staged nor stored (results wrong)
+                    if (false) {
+#else
                     if (live) {
+#endif
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
                             const int k = kbase + rd * 16 + c;
@@ -644,15 +741,21 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapX1, const __grid_c
                     bool stored = true;
                     if (elected) {
                         stored = mbar_wait(ywritten_bar(half), st_use & 1u, abort_flag, 0x580u | ew, prm.spin_limit);
+#ifdef WG_KO_Y
+                        if (false) {
+#else
                         if (stored && kbase + rd * 16 < prm.K) {      // a box that starts beyond the last channel is not issued at all
+#endif
                             if (prm.accumulate) tma_reduce_add_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
                             else tma_store_4d(smem_u32(stage), &mapY, 2 * seg * prm.TW, 2 * rb * TH + a, kbase + rd * 16, g * prm.NB);
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
+                        // (an empty group when nothing was issued: the count of groups per round stays the same)
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                     // the warp goes on together (tcgen05.ld is next) and with one verdict
                     if (!__all_sync(0xffffffffu, stored)) { ok = false; break; }
                     ++st_use;
+                    if (++ybox == kFuYBoxes) ybox = 0;
                 }
                 if (!ok) break;
             }
@@ -690,22 +793,26 @@ static bool fused_geometry(FuParams &p)
     p.TW = p.nW <= 32 ? p.nW : 32;
     p.nSeg = cdiv(p.nW, p.TW);
     p.BW = (2 * p.TW + 5 + 3) & ~3;
-    // the larger of the two boxes (2*TH rows x BW x 16 channels x NB images) has to fit an X buffer
-    auto box_bytes = [&](int th, int nb) { return (size_t)p.BW * 2 * th * 16 * 4 * nb; };
+    p.BWY = (2 * p.TW + 3) & ~3;
+    // the larger of the two input boxes ((TH + 1) rows x BW x 16 channels x NB images; the dense one has 2*TH rows of 8
+    // channels) has to fit an X buffer, and the output box (TH rows x BWY x 16 channels x NB images) a staging box
+    auto fits = [&](int th, int nb) {
+        return (size_t)p.BW * (th + 1) * 16 * 4 * nb <= (size_t)kFuXbufBytes && (size_t)p.BWY * th * 16 * 4 * nb <= (size_t)kFuYStageBytes;
+    };
     p.lp_log2 = 0;
     while ((1 << p.lp_log2) < p.TW) ++p.lp_log2;
     const int max_rows = kBlockM >> p.lp_log2;              // tile rows (of all images) per unit
     int TH = max_rows;
     if (TH > p.nH) TH = p.nH;
-    while (TH > 1 && box_bytes(TH, 1) > (size_t)kFuXbufBytes) --TH;
-    if (box_bytes(TH, 1) > (size_t)kFuXbufBytes) return false;
+    while (TH > 1 && !fits(TH, 1)) --TH;
+    if (!fits(TH, 1)) return false;
     p.nRB = cdiv(p.nH, TH);
     TH = cdiv(p.nH, p.nRB);                  // same number of row blocks, evened out
     p.TH = TH;
     p.NB = 1;
     if (TH == p.nH) {
         int nb = max_rows / TH;
-        while (nb > 1 && box_bytes(TH, nb) > (size_t)kFuXbufBytes) --nb;
+        while (nb > 1 && !fits(TH, nb)) --nb;
         if (nb > p.B) nb = p.B;
         p.NB = nb < 1 ? 1 : nb;
     }
@@ -713,8 +820,7 @@ static bool fused_geometry(FuParams &p)
     p.nGroups = cdiv(p.B, p.NB);
     p.nKB = cdiv(p.K, kBlockN);
     p.nC32 = cdiv(p.C, 32);
-    p.BWY = (2 * p.TW + 3) & ~3;
-    p.xbytes1 = (uint32_t)((size_t)p.BW * 2 * TH * 16 * p.NB * 4);
+    p.xbytes1 = (uint32_t)((size_t)p.BW * 2 * TH * 8 * p.NB * 4);
     p.xbytes2 = (uint32_t)((size_t)p.BW * (TH + 1) * 16 * p.NB * 4);
     const long long units = (long long)p.nGroups * p.nRB * p.nSeg * p.nKB;
     if (units > 0x7fffffffLL) return false;
@@ -748,12 +854,12 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
     p.drop_load = take_drop_load();
     EncodeTiledFn fn = encode_fn();
     if (!fn) return WG2X2_ERR_LAUNCH;
-    CUtensorMap mapX1, mapX2, mapW, mapY;
+    CUtensorMap mapX1, mapX2, mapW, mapW2, mapY;
     {
         cuuint64_t dims[4] = {(cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C, (cuuint64_t)B};
         cuuint64_t strides[3] = {(cuuint64_t)W * 4, (cuuint64_t)H * W * 4, (cuuint64_t)C * H * W * 4};
-        // dense box: rows 2*th0 .. 2*th0 + 2*TH - 1
-        cuuint32_t box1[4] = {(cuuint32_t)p.BW, (cuuint32_t)(2 * p.TH), 16, (cuuint32_t)p.NB};
+        // dense box of 8 channels: rows 2*th0 .. 2*th0 + 2*TH - 1
+        cuuint32_t box1[4] = {(cuuint32_t)p.BW, (cuuint32_t)(2 * p.TH), 8, (cuuint32_t)p.NB};
         cuuint32_t estr1[4] = {1, 1, 1, 1};
         if (fn(&mapX1, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(X), dims, strides, box1, estr1,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -774,6 +880,12 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
         cuuint32_t estr[3] = {1, 1, 1};
         if (fn(&mapW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(prepared), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return WG2X2_ERR_LAUNCH;
+        // phase B: the eight positions of Winograd rows 1 and 2, 16 channels each, rows of 64 bytes (64-byte swizzle)
+        cuuint32_t box2[3] = {16, (cuuint32_t)kBlockN, 8};
+        if (fn(&mapW2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(prepared), dims, strides, box2, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return WG2X2_ERR_LAUNCH;
     }
@@ -808,7 +920,7 @@ int layer_fwd_fused(const float *X, const void *prepared, float *Y, int B, int H
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-        return cudaLaunchKernelEx(&cfg, kernel, mapX1, mapX2, mapW, mapY, p) == cudaSuccess;
+        return cudaLaunchKernelEx(&cfg, kernel, mapX1, mapX2, mapW, mapW2, mapY, p) == cudaSuccess;
     };
     const bool launched = extras ? (affine ? launch(layer_fwd_fused_kernel<true, true>) : launch(layer_fwd_fused_kernel<true, false>))
                                  : (affine ? launch(layer_fwd_fused_kernel<false, true>) : launch(layer_fwd_fused_kernel<false, false>));
