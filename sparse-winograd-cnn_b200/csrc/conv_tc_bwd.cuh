@@ -279,6 +279,7 @@ struct GgParams {
     //   map_mode 0: every chunk runs
     const unsigned long long *block_map;
     int map_mode, map_nkb;
+    int tma_out;             // results that need no mask leave by TMA store (mapOut) straight from the staging block
 };
 
 // Bit n of the result is set when contraction chunk n (32 elements) of this unit has to run: the first chunk always
@@ -318,9 +319,18 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr)
     return d;
 }
 
+// shared memory -> global, clipped to the tensor; completion is tracked by the thread's bulk async-groups
+__device__ __forceinline__ void tma_store_3d(uint32_t src, const CUtensorMap *map, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%1, {%2, %3, %4}], [%0];"
+        ::"r"(src), "l"(map), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kTcThreads, 1)
-conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GgParams prm)
+conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                         const __grid_constant__ CUtensorMap mapOut, const GgParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -481,7 +491,27 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) tmem_ld8(taddr + (uint32_t)(ch * 8), &r[ch * 8]);
                 tmem_ld_wait();
-                if (vec) {
+                if (vec && prm.tma_out && !use_mask) {
+                    // The staging block (32 rows of 128 bytes, 16-byte chunk index XORed with row & 7) is exactly TMA's
+                    // 128-byte swizzle: one lane hands it to a TMA store, which also clips the rows beyond the tensor; the
+                    // block is not read back through the load/store unit, whose shared-memory traffic competes with the
+                    // tensor core's operand reads.  The store that last used the block must have read it first.
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+#pragma unroll
+                    for (int c8 = 0; c8 < 8; ++c8)
+                        *reinterpret_cast<float4 *>(stg + lane * 32 + ((c8 ^ (lane & 7)) << 2)) =
+                            make_float4(r[4 * c8], r[4 * c8 + 1], r[4 * c8 + 2], r[4 * c8 + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_3d(smem_u32(stg), &mapOut, col, rb * 128 + q * 32, (prm.direct ? 0 : split * 16) + t);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                } else if (vec) {
+                    if (prm.tma_out) {      // a TMA store of an earlier block may still be reading the staging block
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
                     __syncwarp();
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8)
@@ -518,6 +548,8 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
             if (lane == 0) mbar_arrive(acce_bar(buf));
             buf ^= 1;
         }
+        // the last stores must have reached memory before the CTA ends
+        if (prm.tma_out && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     tc_fence_before();
@@ -560,13 +592,32 @@ int conv_dw_tc_splits(long long P, int C, int K)
     return (int)cdivll(chunks, cps);
 }
 
+// 3-D map over the result (planes, rows, cols) fp32, cols contiguous, for the epilogue's TMA stores: box = 32 columns x 32
+// rows with the 128-byte swizzle.  Usable when the base is 16-byte aligned and the rows are multiples of 16 bytes.
+static bool make_map_out(CUtensorMap *map, float *ptr, long long cols, long long rows, long long planes)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(ptr) & 15u) || (cols & 3)) return false;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)planes};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)rows * cols * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int KIND>
-static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, const GgParams &prm, cudaStream_t st)
+static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, GgParams &prm, cudaStream_t st)
 {
     if (cudaFuncSetAttribute(conv_grad_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgSmemBytes) != cudaSuccess)
         return WG2X2_ERR_LAUNCH;
+    // results without a mask leave by TMA store where the output can be described to TMA (else: the load/store path)
+    CUtensorMap mapOut = mapA;
+    const bool needs_mask = prm.mask && (KIND == 1 || prm.direct);
+    prm.tma_out = (!needs_mask && prm.cols >= 32 &&
+                   make_map_out(&mapOut, prm.out, prm.cols, prm.rows, 16LL * (prm.direct ? 1 : prm.splits))) ? 1 : 0;
     const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
-    conv_grad_gemm_tc_kernel<KIND><<<grid, kTcThreads, kGgSmemBytes, st>>>(mapA, mapB, prm);
+    conv_grad_gemm_tc_kernel<KIND><<<grid, kTcThreads, kGgSmemBytes, st>>>(mapA, mapB, mapOut, prm);
     return launch_status();
 }
 
