@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstring>
 
 #include "wg_common.cuh"
 
@@ -592,7 +593,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static EncodeTiledFn encode_fn()
+static EncodeTiledFn encode_fn_raw()
 {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {
@@ -604,6 +605,44 @@ static EncodeTiledFn encode_fn()
     }
     return fn;
 }
+
+// cuTensorMapEncodeTiled behind a small per-thread cache keyed by every argument: a layer that is called again on
+// the same buffers (the usual case: a network's activations live at fixed addresses from step to step) finds its
+// maps instead of encoding up to five of them per launch, which matters where a launch is only a few microseconds
+// of GPU time.  A tensor map holds no state but its arguments, so a hit is exact.
+struct MapKey {
+    const void *ptr;
+    cuuint64_t dims[5], strides[4];
+    cuuint32_t box[5], estr[5];
+    int rank, dtype, interleave, swizzle, promo, oob;
+};
+static CUresult encode_cached(CUtensorMap *map, CUtensorMapDataType dtype, cuuint32_t rank, void *ptr, const cuuint64_t *dims,
+                              const cuuint64_t *strides, const cuuint32_t *box, const cuuint32_t *estr, CUtensorMapInterleave il,
+                              CUtensorMapSwizzle sw, CUtensorMapL2promotion promo, CUtensorMapFloatOOBfill oob)
+{
+    constexpr int kEntries = 64;
+    struct Entry { MapKey key; CUtensorMap map; bool used; };
+    thread_local Entry cache[kEntries];
+    thread_local int next = 0;
+    if (rank < 1 || rank > 5) return CUDA_ERROR_INVALID_VALUE;
+    MapKey k;
+    memset(&k, 0, sizeof(k));
+    k.ptr = ptr; k.rank = (int)rank; k.dtype = (int)dtype; k.interleave = (int)il; k.swizzle = (int)sw; k.promo = (int)promo; k.oob = (int)oob;
+    for (cuuint32_t d = 0; d < rank; ++d) { k.dims[d] = dims[d]; k.box[d] = box[d]; k.estr[d] = estr[d]; }
+    for (cuuint32_t d = 0; d + 1 < rank; ++d) k.strides[d] = strides[d];
+    for (int e = 0; e < kEntries; ++e)
+        if (cache[e].used && memcmp(&cache[e].key, &k, sizeof(k)) == 0) { *map = cache[e].map; return CUDA_SUCCESS; }
+    EncodeTiledFn fn = encode_fn_raw();
+    if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+    const CUresult r = fn(map, dtype, rank, ptr, dims, strides, box, estr, il, sw, promo, oob);
+    if (r == CUDA_SUCCESS) {
+        Entry &en = cache[next];
+        next = (next + 1) % kEntries;
+        en.key = k; en.map = *map; en.used = true;
+    }
+    return r;
+}
+static EncodeTiledFn encode_fn() { return encode_fn_raw() ? &encode_cached : nullptr; }
 
 // 3-D map over a (16, rows, C) fp32 tensor, C contiguous: box = 32 x box_rows x 1, 128-B swizzle,
 // out-of-range elements read as zero.
