@@ -213,6 +213,16 @@ int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y,
                                  const float *out_shift, const float *residual, void *stream);
 
 /*
+ * 3x3 / stride 2 max-pooling with TensorFlow's SAME padding on an NCHW tensor (B,C,H,W) -> (B,C,ceil(H/2),ceil(W/2)):
+ * the MaxPooling('pool*', l, 3, stride=2, padding='SAME') steps between the stages of the reference's ResNet-18-var
+ * graph (ResNet-18-var/imagenet-resnet-transWino-prune.py:115,141,166,191).  Y_relu, when not NULL, also receives
+ * max(relu_scale[c] * Y + relu_shift[c], 0) (scale 1 and shift 0 when those are NULL): what the next stage's shortcut
+ * branch starts from -- BNReLU in the first stage (:126), a plain ReLU later (:151) -- so it costs no pass of its own.
+ */
+int wg2x2_maxpool3x3s2_same(const float *X, float *Y, float *Y_relu, const float *relu_scale, const float *relu_shift,
+                            int B, int C, int H, int W, void *stream);
+
+/*
  * Status word of the most recent kernel on this device that uses bounded waits
  * (the tcgen05 path): 0, or WG2X2_ERR_TIMEOUT with a code saying where it gave up.
  * Synchronises the given stream.

@@ -1,0 +1,117 @@
+// 3x3 / stride 2 max-pooling with TensorFlow's SAME padding on NCHW tensors, the down-sampling step between the
+// stages of the reference's ResNet-18-var graph (MaxPooling('pool*', l, 3, stride=2, padding='SAME'),
+// ResNet-18-var/imagenet-resnet-transWino-prune.py:115,141,166,191).  HBM-bound: every input element is read once
+// from memory (the overlap of neighbouring windows is served by registers and L1), every output written once; an
+// optional second output holds relu(pooled), which the next stage's shortcut branch starts from, so that it costs
+// no pass of its own; with a per-channel scale and shift it is relu(scale * pooled + shift), the BNReLU the first
+// stage's shortcut starts from (:126-127).
+//
+// SAME padding: the output has ceil(H/2) x ceil(W/2) pixels; for an even size the window of output i covers input
+// 2i .. 2i+2 (one row/column of padding at the far end only), for an odd size 2i-1 .. 2i+1.  Padding never wins the
+// maximum (it counts as -inf).
+#include "wg_common.cuh"
+
+namespace wg {
+
+// Four consecutive outputs of a row per thread: input columns 8t .. 8t+8 of three rows = two 16-byte loads and one
+// scalar per row.  Needs an even W that is a multiple of 8 and 16-byte aligned tensors.
+template <bool RELU_OUT>
+__global__ void __launch_bounds__(256) maxpool_vec_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
+                                                            const float *__restrict__ rs, const float *__restrict__ rb, int C,
+                                                            long long planes, int H, int W, int OH, int OW, int ph)
+{
+    const int OW4 = OW >> 2;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = planes * OH * OW4;
+    if (idx >= total) return;
+    const int t = (int)(idx % OW4);
+    const int oh = (int)((idx / OW4) % OH);
+    const long long pl = idx / ((long long)OW4 * OH);
+    const float *xp = X + pl * H * W;
+    const float ninf = -__int_as_float(0x7f800000);
+    float m[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) m[k] = ninf;
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+        const int h = 2 * oh - ph + dy;
+        if (h < 0 || h >= H) continue;
+        const float *row = xp + (long long)h * W + 8 * t;
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(row));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(row) + 1);
+        const float c = (8 * t + 8 < W) ? __ldg(row + 8) : ninf;
+        m[0] = fmaxf(m[0], a.x); m[1] = fmaxf(m[1], a.y); m[2] = fmaxf(m[2], a.z); m[3] = fmaxf(m[3], a.w);
+        m[4] = fmaxf(m[4], b.x); m[5] = fmaxf(m[5], b.y); m[6] = fmaxf(m[6], b.z); m[7] = fmaxf(m[7], b.w);
+        m[8] = fmaxf(m[8], c);
+    }
+    float4 o;
+    o.x = fmaxf(fmaxf(m[0], m[1]), m[2]);
+    o.y = fmaxf(fmaxf(m[2], m[3]), m[4]);
+    o.z = fmaxf(fmaxf(m[4], m[5]), m[6]);
+    o.w = fmaxf(fmaxf(m[6], m[7]), m[8]);
+    const long long off = (pl * OH + oh) * OW + 4 * t;
+    *reinterpret_cast<float4 *>(Y + off) = o;
+    if (RELU_OUT) {
+        const float sc = rs ? __ldg(rs + (int)(pl % C)) : 1.f, sh = rs ? __ldg(rb + (int)(pl % C)) : 0.f;
+        *reinterpret_cast<float4 *>(Yr + off) = make_float4(fmaxf(fmaf(o.x, sc, sh), 0.f), fmaxf(fmaf(o.y, sc, sh), 0.f),
+                                                            fmaxf(fmaf(o.z, sc, sh), 0.f), fmaxf(fmaf(o.w, sc, sh), 0.f));
+    }
+}
+
+// Any size: one output per thread.
+template <bool RELU_OUT>
+__global__ void __launch_bounds__(256) maxpool_any_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
+                                                            const float *__restrict__ rs, const float *__restrict__ rb, int C,
+                                                            long long planes, int H, int W, int OH, int OW, int ph, int pw)
+{
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= planes * OH * OW) return;
+    const int ow = (int)(idx % OW);
+    const int oh = (int)((idx / OW) % OH);
+    const long long pl = idx / ((long long)OW * OH);
+    const float *xp = X + pl * H * W;
+    float m = -__int_as_float(0x7f800000);
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+        const int h = 2 * oh - ph + dy;
+        if (h < 0 || h >= H) continue;
+#pragma unroll
+        for (int dx = 0; dx < 3; ++dx) {
+            const int w = 2 * ow - pw + dx;
+            if (w >= 0 && w < W) m = fmaxf(m, __ldg(xp + (long long)h * W + w));
+        }
+    }
+    Y[idx] = m;
+    if (RELU_OUT) Yr[idx] = fmaxf(rs ? fmaf(m, __ldg(rs + (int)(pl % C)), __ldg(rb + (int)(pl % C))) : m, 0.f);
+}
+
+int maxpool3x3s2_same(const float *X, float *Y, float *Yrelu, const float *rs, const float *rb, int B, int C, int H, int W,
+                      cudaStream_t st)
+{
+    if (!X || !Y || B <= 0 || C <= 0 || H <= 0 || W <= 0) return WG2X2_ERR_BAD_ARG;
+    if ((rs == nullptr) != (rb == nullptr) || (rs && !Yrelu)) return WG2X2_ERR_BAD_ARG;
+    const int OH = (H + 1) / 2, OW = (W + 1) / 2, ph = H & 1, pw = W & 1;
+    const long long planes = (long long)B * C;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if ((W % 8) == 0 && al16(X) && al16(Y) && (!Yrelu || al16(Yrelu))) {
+        const long long total = planes * OH * (OW / 4);
+        const long long blocks = cdivll(total, 256);
+        if (blocks > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
+        if (Yrelu) maxpool_vec_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
+        else       maxpool_vec_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
+    } else {
+        const long long blocks = cdivll(planes * OH * OW, 256);
+        if (blocks > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
+        if (Yrelu) maxpool_any_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph, pw);
+        else       maxpool_any_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph, pw);
+    }
+    return launch_status();
+}
+
+}  // namespace wg
+
+extern "C" int wg2x2_maxpool3x3s2_same(const float *X, float *Y, float *Y_relu, const float *relu_scale, const float *relu_shift,
+                                       int B, int C, int H, int W, void *stream)
+{
+    return wg::maxpool3x3s2_same(X, Y, Y_relu, relu_scale, relu_shift, B, C, H, W, (cudaStream_t)stream);
+}

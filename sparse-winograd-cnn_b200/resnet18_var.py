@@ -7,8 +7,8 @@ the `a` blocks carry a 1x1 shortcut convolution + BatchNorm, the `b` blocks an i
 after a ReLU.  The reference has `pool4` commented out (:191), so its stage 5 runs at 14x14;
 `stage5_pool=True` restores the pool (7x7), which is the shape the benchmark configuration names.
 
-Only the Winograd layers run on this repository's kernels; the stem, pools, 1x1 shortcuts and the classifier
-are stock torch ops.  With layout="NCHW" the layers of the two high-resolution stages (56x56 and 28x28) run
+The Winograd layers and (for NCHW activations) the max-pools run on this repository's kernels; the stem, 1x1
+shortcuts and the classifier are stock torch ops.  With layout="NCHW" the layers of the two high-resolution stages (56x56 and 28x28) run
 as one kernel each, BatchNorms and shortcut add included.  Weights are random (seeded): there is
 no checkpoint to load here.
 """
@@ -168,17 +168,34 @@ class ResNet18Var(torch.nn.Module):
             x = x.contiguous(memory_format=torch.channels_last)
             stem = stem.contiguous(memory_format=torch.channels_last)
         l = F.conv2d(x, stem, stride=2)
-        l = _same_pool(l)
+        # the pools between the stages: this library's kernel on NCHW activations (it also hands out relu(pooled), which
+        # the next stage's shortcut branch starts from), torch's elsewhere
+        own_pool = not reference and self.layout == "NCHW" and l.is_cuda
+        l_relu = None
+        if own_pool:       # pool1, and relu(BN(pool1)) for the first stage's shortcut from the same pass
+            pre = self.blocks[0][0]["pre"]
+            l, l_relu = wg2x2.maxpool3x3s2_same(l.contiguous(), with_relu=True, relu_scale=pre.scale, relu_shift=pre.shift)
+        else:
+            l = _same_pool(l)
         for s, (blk_a, blk_b) in enumerate(self.blocks):
-            main = torch.relu(blk_a["pre"](l)) if s == 0 else torch.relu(l)
+            if l_relu is not None:
+                main = l_relu
+            else:
+                main = torch.relu(blk_a["pre"](l)) if s == 0 else torch.relu(l)
             if reference or not self.fused:
                 main = blk_a["bn1"](F.conv2d(main, blk_a.short))
-            else:   # the BatchNorm after the 1x1 shortcut folds into its weights and bias
-                main = F.conv2d(main, blk_a.short * blk_a["bn1"].scale.view(-1, 1, 1, 1), bias=blk_a["bn1"].shift)
+            else:   # the BatchNorm after the 1x1 shortcut folds into its weights (once) and bias
+                if getattr(blk_a, "_short_folded", None) is None or blk_a._short_folded.device != blk_a.short.device:
+                    blk_a._short_folded = (blk_a.short * blk_a["bn1"].scale.view(-1, 1, 1, 1)).detach()
+                main = F.conv2d(main, blk_a._short_folded, bias=blk_a["bn1"].shift)
             l = self._block(blk_a, l, main, reference)
             l = self._block(blk_b, l, torch.relu(l), reference)
+            l_relu = None
             if s < 2 or (s == 2 and self.stage5_pool):
-                l = _same_pool(l)
+                if own_pool:
+                    l, l_relu = wg2x2.maxpool3x3s2_same(l.contiguous(), with_relu=True)
+                else:
+                    l = _same_pool(l)
         l = torch.relu(l).mean(dim=(2, 3))
         return F.linear(l, self.fc_w, self.fc_b)
 

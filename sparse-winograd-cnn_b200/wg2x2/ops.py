@@ -252,6 +252,20 @@ def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shi
     return Y
 
 
+def maxpool3x3s2_same(x, with_relu=False, relu_scale=None, relu_shift=None):
+    """3x3 / stride 2 max-pooling with TensorFlow's SAME padding of an NCHW tensor; with_relu=True returns
+    (pooled, relu(relu_scale[c] * pooled + relu_shift[c])) from the same pass (scale 1, shift 0 when not given)."""
+    _chk(x, "x")
+    B, C, H, W = x.shape
+    _chk_shape(relu_scale, (C,), "relu_scale"); _chk_shape(relu_shift, (C,), "relu_shift")
+    y = torch.empty((B, C, (H + 1) // 2, (W + 1) // 2), dtype=torch.float32, device=x.device)
+    yr = torch.empty_like(y) if with_relu else None
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_maxpool3x3s2_same(_ptr(x), _ptr(y), _ptr(yr), _ptr(relu_scale), _ptr(relu_shift), B, C, H, W,
+                                               _stream()), "wg2x2_maxpool3x3s2_same")
+    return (y, yr) if with_relu else y
+
+
 def last_device_status():
     """(status, where) of the bounded device-side waits since the last reading; synchronises the current stream.
     The tensor-core calls above do not read it themselves (that would cost a synchronisation per call): after a

@@ -57,3 +57,25 @@ def test_same_pool_matches_tensorflow_padding():
         pw = max((-(-W // 2) - 1) * 2 + 3 - W, 0)
         ref = F.max_pool2d(F.pad(x, (pw // 2, pw - pw // 2, ph // 2, ph - ph // 2), value=float("-inf")), 3, 2)
         assert torch.equal(_same_pool(x), ref)
+
+
+@pytest.mark.parametrize("shape", [(3, 8, 112, 112), (2, 5, 56, 56), (2, 4, 28, 28), (2, 3, 14, 14), (2, 3, 7, 7), (1, 2, 14, 9),
+                                   (1, 2, 5, 8), (2, 3, 9, 16), (1, 1, 1, 1), (1, 2, 2, 3)])
+def test_pool_kernel_matches_torch(shape):
+    """wg2x2_maxpool3x3s2_same (the vector path for widths that are multiples of 8, the general path elsewhere, odd
+    sizes included) against the torch form of the same pooling: the maxima bit for bit, the extra ReLU output too, the
+    affine ReLU output to rounding."""
+    import wg2x2
+    from resnet18_var import _same_pool
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    x = torch.randn(shape, device="cuda", generator=g)
+    want = _same_pool(x)
+    got = wg2x2.maxpool3x3s2_same(x)
+    assert torch.equal(got, want)
+    got2, relu = wg2x2.maxpool3x3s2_same(x, with_relu=True)
+    assert torch.equal(got2, want) and torch.equal(relu, torch.relu(want))
+    sc = 1 + 0.2 * torch.randn(shape[1], device="cuda", generator=g)
+    sh = 0.3 * torch.randn(shape[1], device="cuda", generator=g)
+    got3, bnrelu = wg2x2.maxpool3x3s2_same(x, with_relu=True, relu_scale=sc, relu_shift=sh)
+    ref = torch.relu(want * sc.view(1, -1, 1, 1) + sh.view(1, -1, 1, 1))
+    assert torch.equal(got3, want) and float((bnrelu - ref).abs().max()) <= 1e-6 * max(1.0, float(ref.abs().max()))
