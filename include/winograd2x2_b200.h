@@ -221,6 +221,10 @@ int wg2x2_layer_fwd_fused_affine(const float *X, const void *prepared, float *Y,
  */
 int wg2x2_maxpool3x3s2_same(const float *X, float *Y, float *Y_relu, const float *relu_scale, const float *relu_shift,
                             int B, int C, int H, int W, void *stream);
+/* The same pooling of a channels-last input X (B,H,W,C) into NCHW outputs: the step after a stem convolution that runs
+ * channels-last (ResNet-18-var/imagenet-resnet-transWino-prune.py:114-115) when the Winograd layers that follow take NCHW. */
+int wg2x2_maxpool3x3s2_same_nhwc_in(const float *X, float *Y, float *Y_relu, const float *relu_scale,
+                                    const float *relu_shift, int B, int C, int H, int W, void *stream);
 
 /*
  * Status word of the most recent kernel on this device that uses bounded waits

@@ -85,6 +85,62 @@ __global__ void __launch_bounds__(256) maxpool_any_kernel(const float *__restric
     if (RELU_OUT) Yr[idx] = fmaxf(rs ? fmaf(m, __ldg(rs + (int)(pl % C)), __ldg(rb + (int)(pl % C))) : m, 0.f);
 }
 
+// Channels-last input (B,H,W,C), NCHW output: what follows a convolution that runs channels-last (the 7x7 stem is
+// fastest that way) when the next layer wants NCHW.  A block takes one output row of 32 channels: lanes run along the
+// channels for the loads (128 contiguous bytes per pixel), the row is turned through shared memory, and lanes run
+// along the pixels for the stores.
+template <bool RELU_OUT>
+__global__ void __launch_bounds__(256) maxpool_nhwc_in_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
+                                                                const float *__restrict__ rs, const float *__restrict__ rb, int C, int H,
+                                                                int W, int OH, int OW, int ph, int pw, int pitch)
+{
+    extern __shared__ float S[];                    // [32 channels][pitch]
+    const int oh = blockIdx.x % OH, b = blockIdx.x / OH;
+    const int c0 = blockIdx.y * 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool c_ok = c0 + lane < C;
+    const float ninf = -__int_as_float(0x7f800000);
+    for (int ow = warp; ow < OW; ow += 8) {
+        float m = ninf;
+#pragma unroll
+        for (int dy = 0; dy < 3; ++dy) {
+            const int h = 2 * oh - ph + dy;
+            if (h < 0 || h >= H) continue;
+#pragma unroll
+            for (int dx = 0; dx < 3; ++dx) {
+                const int w = 2 * ow - pw + dx;
+                if (w >= 0 && w < W && c_ok) m = fmaxf(m, __ldg(X + (((long long)b * H + h) * W + w) * C + c0 + lane));
+            }
+        }
+        S[lane * pitch + ow] = m;
+    }
+    __syncthreads();
+    for (int c = warp; c < 32 && c0 + c < C; c += 8) {
+        const long long o = (((long long)b * C + c0 + c) * OH + oh) * OW;
+        const float sc = (RELU_OUT && rs) ? __ldg(rs + c0 + c) : 1.f, sh = (RELU_OUT && rs) ? __ldg(rb + c0 + c) : 0.f;
+        for (int ow = lane; ow < OW; ow += 32) {
+            const float v = S[c * pitch + ow];
+            Y[o + ow] = v;
+            if (RELU_OUT) Yr[o + ow] = fmaxf(fmaf(v, sc, sh), 0.f);
+        }
+    }
+}
+
+int maxpool3x3s2_same_nhwc_in(const float *X, float *Y, float *Yrelu, const float *rs, const float *rb, int B, int C, int H, int W,
+                              cudaStream_t st)
+{
+    if (!X || !Y || B <= 0 || C <= 0 || H <= 0 || W <= 0) return WG2X2_ERR_BAD_ARG;
+    if ((rs == nullptr) != (rb == nullptr) || (rs && !Yrelu)) return WG2X2_ERR_BAD_ARG;
+    const int OH = (H + 1) / 2, OW = (W + 1) / 2, ph = H & 1, pw = W & 1;
+    const int pitch = OW | 1;
+    const size_t smem = (size_t)32 * pitch * sizeof(float);
+    if ((long long)B * OH > 0x7fffffffLL || cdiv(C, 32) > 65535 || smem > 48 * 1024) return WG2X2_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)(B * OH), cdiv(C, 32));
+    if (Yrelu) maxpool_nhwc_in_kernel<true><<<grid, 256, smem, st>>>(X, Y, Yrelu, rs, rb, C, H, W, OH, OW, ph, pw, pitch);
+    else       maxpool_nhwc_in_kernel<false><<<grid, 256, smem, st>>>(X, Y, Yrelu, rs, rb, C, H, W, OH, OW, ph, pw, pitch);
+    return launch_status();
+}
+
 int maxpool3x3s2_same(const float *X, float *Y, float *Yrelu, const float *rs, const float *rb, int B, int C, int H, int W,
                       cudaStream_t st)
 {
@@ -109,6 +165,12 @@ int maxpool3x3s2_same(const float *X, float *Y, float *Yrelu, const float *rs, c
 }
 
 }  // namespace wg
+
+extern "C" int wg2x2_maxpool3x3s2_same_nhwc_in(const float *X, float *Y, float *Y_relu, const float *relu_scale, const float *relu_shift,
+                                               int B, int C, int H, int W, void *stream)
+{
+    return wg::maxpool3x3s2_same_nhwc_in(X, Y, Y_relu, relu_scale, relu_shift, B, C, H, W, (cudaStream_t)stream);
+}
 
 extern "C" int wg2x2_maxpool3x3s2_same(const float *X, float *Y, float *Y_relu, const float *relu_scale, const float *relu_shift,
                                        int B, int C, int H, int W, void *stream)

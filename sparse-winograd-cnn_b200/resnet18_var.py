@@ -164,17 +164,19 @@ class ResNet18Var(torch.nn.Module):
         float64 einsums instead of this repository's kernels."""
         x = F.pad(image, (2, 3, 2, 3))                                  # 7x7/2 with TensorFlow's SAME padding
         stem = self.stem
-        if self.layout == "NHWC" and not reference:
+        # the pools between the stages: this library's kernel on NCHW activations (it also hands out relu(pooled), which
+        # the next stage's shortcut branch starts from), torch's elsewhere
+        own_pool = not reference and self.layout == "NCHW" and image.is_cuda
+        if (self.layout == "NHWC" or own_pool) and not reference:
+            # the stem runs channels-last (cuDNN's faster form for it); for NCHW activations the first pool reads that
+            # layout and writes NCHW
             x = x.contiguous(memory_format=torch.channels_last)
             stem = stem.contiguous(memory_format=torch.channels_last)
         l = F.conv2d(x, stem, stride=2)
-        # the pools between the stages: this library's kernel on NCHW activations (it also hands out relu(pooled), which
-        # the next stage's shortcut branch starts from), torch's elsewhere
-        own_pool = not reference and self.layout == "NCHW" and l.is_cuda
         l_relu = None
         if own_pool:       # pool1, and relu(BN(pool1)) for the first stage's shortcut from the same pass
             pre = self.blocks[0][0]["pre"]
-            l, l_relu = wg2x2.maxpool3x3s2_same(l.contiguous(), with_relu=True, relu_scale=pre.scale, relu_shift=pre.shift)
+            l, l_relu = wg2x2.maxpool3x3s2_same(l, with_relu=True, relu_scale=pre.scale, relu_shift=pre.shift)
         else:
             l = _same_pool(l)
         for s, (blk_a, blk_b) in enumerate(self.blocks):

@@ -253,16 +253,20 @@ def layer_fwd_fused(x, prepared, K, relu=True, out=None, out_scale=None, out_shi
 
 
 def maxpool3x3s2_same(x, with_relu=False, relu_scale=None, relu_shift=None):
-    """3x3 / stride 2 max-pooling with TensorFlow's SAME padding of an NCHW tensor; with_relu=True returns
-    (pooled, relu(relu_scale[c] * pooled + relu_shift[c])) from the same pass (scale 1, shift 0 when not given)."""
-    _chk(x, "x")
+    """3x3 / stride 2 max-pooling with TensorFlow's SAME padding of a (B,C,H,W) tensor into NCHW outputs; with_relu=True
+    returns (pooled, relu(relu_scale[c] * pooled + relu_shift[c])) from the same pass (scale 1, shift 0 when not given).
+    x may be contiguous (NCHW) or channels-last (e.g. the output of a channels-last convolution)."""
     B, C, H, W = x.shape
+    entry, name = lib.wg2x2_maxpool3x3s2_same, "wg2x2_maxpool3x3s2_same"
+    if not x.is_contiguous() and x.is_contiguous(memory_format=torch.channels_last) and x.is_cuda and x.dtype == torch.float32:
+        entry, name = lib.wg2x2_maxpool3x3s2_same_nhwc_in, "wg2x2_maxpool3x3s2_same_nhwc_in"
+    else:
+        _chk(x, "x")
     _chk_shape(relu_scale, (C,), "relu_scale"); _chk_shape(relu_shift, (C,), "relu_shift")
     y = torch.empty((B, C, (H + 1) // 2, (W + 1) // 2), dtype=torch.float32, device=x.device)
     yr = torch.empty_like(y) if with_relu else None
     with torch.cuda.device(x.device):
-        _lib.check(lib.wg2x2_maxpool3x3s2_same(_ptr(x), _ptr(y), _ptr(yr), _ptr(relu_scale), _ptr(relu_shift), B, C, H, W,
-                                               _stream()), "wg2x2_maxpool3x3s2_same")
+        _lib.check(entry(_ptr(x), _ptr(y), _ptr(yr), _ptr(relu_scale), _ptr(relu_shift), B, C, H, W, _stream()), name)
     return (y, yr) if with_relu else y
 
 

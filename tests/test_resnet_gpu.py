@@ -79,3 +79,9 @@ def test_pool_kernel_matches_torch(shape):
     got3, bnrelu = wg2x2.maxpool3x3s2_same(x, with_relu=True, relu_scale=sc, relu_shift=sh)
     ref = torch.relu(want * sc.view(1, -1, 1, 1) + sh.view(1, -1, 1, 1))
     assert torch.equal(got3, want) and float((bnrelu - ref).abs().max()) <= 1e-6 * max(1.0, float(ref.abs().max()))
+    # the same from a channels-last input (the layout a channels-last stem convolution leaves): NCHW outputs
+    xcl = x.contiguous(memory_format=torch.channels_last)
+    got4, bnrelu4 = wg2x2.maxpool3x3s2_same(xcl, with_relu=True, relu_scale=sc, relu_shift=sh)
+    assert got4.is_contiguous() and torch.equal(got4, want)
+    assert float((bnrelu4 - ref).abs().max()) <= 1e-6 * max(1.0, float(ref.abs().max()))
+    assert torch.equal(wg2x2.maxpool3x3s2_same(xcl), want)
