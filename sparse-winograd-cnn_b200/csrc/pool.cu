@@ -86,22 +86,23 @@ __global__ void __launch_bounds__(256) maxpool_any_kernel(const float *__restric
 }
 
 // Channels-last input (B,H,W,C), NCHW output: what follows a convolution that runs channels-last (the 7x7 stem is
-// fastest that way) when the next layer wants NCHW.  A block takes one output row of 32 channels: lanes run along the
-// channels for the loads (128 contiguous bytes per pixel), the row is turned through shared memory, and lanes run
-// along the pixels for the stores.
-template <bool RELU_OUT>
+// fastest that way) when the next layer wants NCHW.  A block takes one output row of 32 * VEC channels: lanes run along
+// the channels for the loads (VEC = 2: 256 contiguous bytes per pixel and warp, so that with 64 channels a warp walks
+// whole input rows), the row is turned through shared memory, and lanes run along the pixels for the stores.
+template <int VEC, bool RELU_OUT>
 __global__ void __launch_bounds__(256) maxpool_nhwc_in_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
                                                                 const float *__restrict__ rs, const float *__restrict__ rb, int C, int H,
                                                                 int W, int OH, int OW, int ph, int pw, int pitch)
 {
-    extern __shared__ float S[];                    // [32 channels][pitch]
+    constexpr int CB = 32 * VEC;
+    extern __shared__ float S[];                    // [CB channels][pitch]
     const int oh = blockIdx.x % OH, b = blockIdx.x / OH;
-    const int c0 = blockIdx.y * 32;
+    const int c0 = blockIdx.y * CB;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool c_ok = c0 + lane < C;
+    const bool c_ok = c0 + VEC * lane < C;          // (VEC = 2 is used for even C only: the pair is in or out together)
     const float ninf = -__int_as_float(0x7f800000);
     for (int ow = warp; ow < OW; ow += 8) {
-        float m = ninf;
+        float m0 = ninf, m1 = ninf;
 #pragma unroll
         for (int dy = 0; dy < 3; ++dy) {
             const int h = 2 * oh - ph + dy;
@@ -109,13 +110,18 @@ __global__ void __launch_bounds__(256) maxpool_nhwc_in_kernel(const float *__res
 #pragma unroll
             for (int dx = 0; dx < 3; ++dx) {
                 const int w = 2 * ow - pw + dx;
-                if (w >= 0 && w < W && c_ok) m = fmaxf(m, __ldg(X + (((long long)b * H + h) * W + w) * C + c0 + lane));
+                if (w >= 0 && w < W && c_ok) {
+                    const float *p = X + (((long long)b * H + h) * W + w) * C + c0 + VEC * lane;
+                    if (VEC == 2) { const float2 v = __ldg(reinterpret_cast<const float2 *>(p)); m0 = fmaxf(m0, v.x); m1 = fmaxf(m1, v.y); }
+                    else m0 = fmaxf(m0, __ldg(p));
+                }
             }
         }
-        S[lane * pitch + ow] = m;
+        S[(VEC * lane) * pitch + ow] = m0;
+        if (VEC == 2) S[(VEC * lane + 1) * pitch + ow] = m1;
     }
     __syncthreads();
-    for (int c = warp; c < 32 && c0 + c < C; c += 8) {
+    for (int c = warp; c < CB && c0 + c < C; c += 8) {
         const long long o = (((long long)b * C + c0 + c) * OH + oh) * OW;
         const float sc = (RELU_OUT && rs) ? __ldg(rs + c0 + c) : 1.f, sh = (RELU_OUT && rs) ? __ldg(rb + c0 + c) : 0.f;
         for (int ow = lane; ow < OW; ow += 32) {
@@ -133,11 +139,15 @@ int maxpool3x3s2_same_nhwc_in(const float *X, float *Y, float *Yrelu, const floa
     if ((rs == nullptr) != (rb == nullptr) || (rs && !Yrelu)) return WG2X2_ERR_BAD_ARG;
     const int OH = (H + 1) / 2, OW = (W + 1) / 2, ph = H & 1, pw = W & 1;
     const int pitch = OW | 1;
-    const size_t smem = (size_t)32 * pitch * sizeof(float);
-    if ((long long)B * OH > 0x7fffffffLL || cdiv(C, 32) > 65535 || smem > 48 * 1024) return WG2X2_ERR_UNSUPPORTED;
-    const dim3 grid((unsigned)(B * OH), cdiv(C, 32));
-    if (Yrelu) maxpool_nhwc_in_kernel<true><<<grid, 256, smem, st>>>(X, Y, Yrelu, rs, rb, C, H, W, OH, OW, ph, pw, pitch);
-    else       maxpool_nhwc_in_kernel<false><<<grid, 256, smem, st>>>(X, Y, Yrelu, rs, rb, C, H, W, OH, OW, ph, pw, pitch);
+    const bool vec2 = (C % 2 == 0) && C >= 64 && (reinterpret_cast<uintptr_t>(X) & 7u) == 0;
+    const int cb = vec2 ? 64 : 32;
+    const size_t smem = (size_t)cb * pitch * sizeof(float);
+    if ((long long)B * OH > 0x7fffffffLL || cdiv(C, cb) > 65535 || smem > 48 * 1024) return WG2X2_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)(B * OH), cdiv(C, cb));
+#define WG_POOL_LAUNCH(V, R) maxpool_nhwc_in_kernel<V, R><<<grid, 256, smem, st>>>(X, Y, Yrelu, rs, rb, C, H, W, OH, OW, ph, pw, pitch)
+    if (vec2) { if (Yrelu) WG_POOL_LAUNCH(2, true); else WG_POOL_LAUNCH(2, false); }
+    else      { if (Yrelu) WG_POOL_LAUNCH(1, true); else WG_POOL_LAUNCH(1, false); }
+#undef WG_POOL_LAUNCH
     return launch_status();
 }
 

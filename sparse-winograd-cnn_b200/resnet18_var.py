@@ -42,6 +42,13 @@ class _BN(torch.nn.Module):
         return x * self.scale.view(1, -1, 1, 1) + self.shift.view(1, -1, 1, 1)
 
 
+class _Affine:
+    """A (scale, shift) pair in the shape the layer calls take a BatchNorm."""
+
+    def __init__(self, scale, shift):
+        self.scale, self.shift = scale, shift
+
+
 class _WinogradLayer(torch.nn.Module):
     """WinogradImTrans(relu) + WinogradConv with a fixed pruning mask."""
 
@@ -145,15 +152,24 @@ class ResNet18Var(torch.nn.Module):
         self.fc_w = torch.nn.Parameter(torch.randn((num_classes, 512), generator=gen) * (1.0 / 512) ** 0.5, requires_grad=False)
         self.fc_b = torch.nn.Parameter(torch.zeros(num_classes), requires_grad=False)
 
-    def _block(self, blk, l, main, ref):
-        """main + bn2c(conv(bn2b(conv(bn2a(l))))) with the Winograd layers as `ref` says."""
+    def _block(self, blk, l, main, ref, main_bias=None):
+        """main [+ main_bias] + bn2c(conv(bn2b(conv(bn2a(l))))) with the Winograd layers as `ref` says.  main_bias is a
+        per-channel constant still owed to `main` (the folded BatchNorm shift of the 1x1 shortcut): on the fused path it
+        rides on the last kernel's output shift instead of costing a pass over `main`."""
         if not ref and self.math == "tf32" and self.fused:
             wa, wb = blk["w2a"], blk["w2b"]
             t = (wa.forward_onekernel(l, blk["bn2a"]) if wa.onekernel_pays(l, self.layout)
                  else wa.forward_fused(l, blk["bn2a"], layout=self.layout))
+            bn_out = blk["bn2c"]
+            if main_bias is not None:
+                if getattr(blk, "_out_folded", None) is None or blk._out_folded.shift.device != bn_out.shift.device:
+                    blk._out_folded = _Affine(bn_out.scale, (bn_out.shift + main_bias).detach())
+                bn_out = blk._out_folded
             if wb.onekernel_pays(t, self.layout):
-                return wb.forward_onekernel(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main)
-            return wb.forward_fused(t, blk["bn2b"], bn_out=blk["bn2c"], residual=main, layout=self.layout)
+                return wb.forward_onekernel(t, blk["bn2b"], bn_out=bn_out, residual=main)
+            return wb.forward_fused(t, blk["bn2b"], bn_out=bn_out, residual=main, layout=self.layout)
+        if main_bias is not None:
+            main = main + main_bias.view(1, -1, 1, 1)
         conv = (lambda m, t: m.forward_reference(t)) if ref else (lambda m, t: m(t, self.math, self.layout))
         t = conv(blk["w2a"], blk["bn2a"](l))
         t = conv(blk["w2b"], blk["bn2b"](t))
@@ -162,16 +178,22 @@ class ResNet18Var(torch.nn.Module):
     def forward(self, image, reference=False):
         """image: (B,3,H,W) float32, already normalised.  reference=True computes the Winograd layers with
         float64 einsums instead of this repository's kernels."""
-        x = F.pad(image, (2, 3, 2, 3))                                  # 7x7/2 with TensorFlow's SAME padding
         stem = self.stem
         # the pools between the stages: this library's kernel on NCHW activations (it also hands out relu(pooled), which
         # the next stage's shortcut branch starts from), torch's elsewhere
         own_pool = not reference and self.layout == "NCHW" and image.is_cuda
         if (self.layout == "NHWC" or own_pool) and not reference:
             # the stem runs channels-last (cuDNN's faster form for it); for NCHW activations the first pool reads that
-            # layout and writes NCHW
-            x = x.contiguous(memory_format=torch.channels_last)
-            stem = stem.contiguous(memory_format=torch.channels_last)
+            # layout and writes NCHW.  7x7/2 with TensorFlow's SAME padding (2 before, 3 after), written straight
+            # into a channels-last buffer
+            B_, C_, H_, W_ = image.shape
+            x = torch.empty((B_, C_, H_ + 5, W_ + 5), dtype=image.dtype, device=image.device, memory_format=torch.channels_last).zero_()
+            x[:, :, 2:2 + H_, 2:2 + W_].copy_(image)
+            if getattr(self, "_stem_cl", None) is None or self._stem_cl.device != stem.device:
+                self._stem_cl = stem.detach().contiguous(memory_format=torch.channels_last)
+            stem = self._stem_cl
+        else:
+            x = F.pad(image, (2, 3, 2, 3))
         l = F.conv2d(x, stem, stride=2)
         l_relu = None
         if own_pool:       # pool1, and relu(BN(pool1)) for the first stage's shortcut from the same pass
@@ -189,8 +211,8 @@ class ResNet18Var(torch.nn.Module):
             else:   # the BatchNorm after the 1x1 shortcut folds into its weights (once) and bias
                 if getattr(blk_a, "_short_folded", None) is None or blk_a._short_folded.device != blk_a.short.device:
                     blk_a._short_folded = (blk_a.short * blk_a["bn1"].scale.view(-1, 1, 1, 1)).detach()
-                main = F.conv2d(main, blk_a._short_folded, bias=blk_a["bn1"].shift)
-            l = self._block(blk_a, l, main, reference)
+                main = F.conv2d(main, blk_a._short_folded)      # its shift is added by the block's last kernel
+            l = self._block(blk_a, l, main, reference, main_bias=None if (reference or not self.fused) else blk_a["bn1"].shift)
             l = self._block(blk_b, l, torch.relu(l), reference)
             l_relu = None
             if s < 2 or (s == 2 and self.stage5_pool):
