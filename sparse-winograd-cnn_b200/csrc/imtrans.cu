@@ -483,6 +483,89 @@ __global__ void __launch_bounds__(256, 4) imtrans_bwd_nchw_band_kernel(const flo
     }
 }
 
+
+// NCHW, small images (a whole image of 128 or 64 channels fits shared memory): every value of dV is read from memory
+// exactly once.  A block takes one image x CB channels; a warp takes one tile x 32 channels at a time (lane = channel:
+// sixteen coalesced 128-byte loads), turns its sixteen gradients into the 4 x 4 window B g B^T and adds the window
+// into the block's image in shared memory.  Windows of tiles two apart do not overlap, so the tiles are walked in four
+// passes by the parity of (tile row, tile column) with a barrier between passes, and plain read-modify-writes suffice
+// (no atomics: the result does not depend on the order of the warps).  The image is kept as [channel][pixel] with an
+// odd pitch (lanes hit distinct banks) and leaves as one contiguous run: CB channels x H*W pixels are adjacent in dX.
+template <bool MASK>
+__global__ void __launch_bounds__(256) imtrans_bwd_nchw_image_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                       float *__restrict__ dX, int B, int H, int W, int C, int nH, int nW,
+                                                                       int CB, int pitch)
+{
+    extern __shared__ float O[];                   // [CB][pitch]
+    const int b = blockIdx.x, c0 = blockIdx.y * CB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int HW = H * W;
+    const int nch = min(CB, C - c0);
+    const int ngr = (nch + 31) >> 5;               // groups of 32 channels
+    const long long plane = (long long)B * nH * nW * C;
+    for (int k = threadIdx.x; k < CB * pitch; k += 256) O[k] = 0.f;
+    __syncthreads();
+#pragma unroll 1
+    for (int pc = 0; pc < 4; ++pc) {
+        const int pr = pc >> 1, pq = pc & 1;
+        const int ntr = (nH - pr + 1) >> 1, ntc = (nW - pq + 1) >> 1;
+        const int items = ntr * ntc * ngr;
+#pragma unroll 1
+        for (int it = warp; it < items; it += 8) {
+            const int gr = it % ngr, tt = it / ngr;
+            const int th = 2 * (tt / ntc) + pr, tw = 2 * (tt % ntc) + pq;
+            const int cl = gr * 32 + lane;
+            if (cl < nch) {
+                const long long base = (((long long)b * nH + th) * nW + tw) * C + c0 + cl;
+                float g[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) g[i][j] = __ldg(dV + (long long)(4 * i + j) * plane + base);
+                if (MASK) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (!(__ldg(Vm + (long long)(4 * i + j) * plane + base) > 0.f)) g[i][j] = 0.f;
+                }
+                // d = B g B^T, B[y][i] = Bt[i][y]: along one axis (u0..u3) -> (u0, u1 - u2 + u3, -u0 + u1 + u2, -u3)
+                float r[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    r[0][j] = g[0][j];
+                    r[1][j] = g[1][j] - g[2][j] + g[3][j];
+                    r[2][j] = g[1][j] + g[2][j] - g[0][j];
+                    r[3][j] = -g[3][j];
+                }
+                float *o = O + cl * pitch;
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const int h = 2 * th - 1 + y;
+                    if (h < 0 || h >= H) continue;
+                    const float d0 = r[y][0], d1 = r[y][1] - r[y][2] + r[y][3], d2 = r[y][1] + r[y][2] - r[y][0], d3 = -r[y][3];
+                    const int w0 = 2 * tw - 1;
+                    float *row = o + h * W;
+                    if (w0 >= 0) row[w0] += d0;
+                    row[w0 + 1] += d1;
+                    if (w0 + 2 < W) row[w0 + 2] += d2;
+                    if (w0 + 3 < W) row[w0 + 3] += d3;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float *dst = dX + ((long long)b * C + c0) * HW;
+    if (pitch == HW) {
+        for (int k = threadIdx.x; k < nch * HW; k += 256) dst[k] = O[k];
+    } else {
+        for (int k = threadIdx.x; k < nch * HW; k += 256) {
+            const int c = k / HW;
+            dst[k] = O[c * pitch + (k - c * HW)];
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
@@ -575,6 +658,26 @@ int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W
             else    imtrans_bwd_nhwc_kernel<1, false><<<g, 256, 0, st>>>(dV, Vm, dX, B, H, W, C, nH, nW);
         }
     } else {
+        // small images: one block per image and channel block, every value of dV read once
+        const int HW = H * W;
+        if (HW <= 200 && (long long)B * cdiv(C, HW <= 64 ? 128 : 64) >= 2LL * kNumSMs && B <= 0x7fffffff) {
+            const int CB = HW <= 64 ? 128 : 64;
+            const int pitch = HW | 1;
+            const int smem = CB * pitch * (int)sizeof(float);
+            if (cdiv(C, CB) <= 65535) {
+                const dim3 grid((unsigned)B, cdiv(C, CB));
+                if (Vm) {
+                    if (cudaFuncSetAttribute(imtrans_bwd_nchw_image_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                        return WG2X2_ERR_LAUNCH;
+                    imtrans_bwd_nchw_image_kernel<true><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, CB, pitch);
+                } else {
+                    if (cudaFuncSetAttribute(imtrans_bwd_nchw_image_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+                        return WG2X2_ERR_LAUNCH;
+                    imtrans_bwd_nchw_image_kernel<false><<<grid, 256, smem, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, CB, pitch);
+                }
+                return launch_status();
+            }
+        }
         if (W <= 192) {
             // four channels per lane (16-byte loads) where the channels allow it and a band of 128 channels stays small
             // four channels per lane (16-byte loads) where the channels allow it; 128 channels per block where a band of
