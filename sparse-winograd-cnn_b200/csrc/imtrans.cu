@@ -509,25 +509,40 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_image_kernel(const float
     for (int pc = 0; pc < 4; ++pc) {
         const int pr = pc >> 1, pq = pc & 1;
         const int ntr = (nH - pr + 1) >> 1, ntc = (nW - pq + 1) >> 1;
-        const int items = ntr * ntc * ngr;
+        const int ntiles = ntr * ntc;
+        // (tile, channel group) pairs go round the eight warps; with 1, 2, 4 or 8 groups a warp keeps its group and
+        // walks the tiles with a fixed stride, which keeps divisions out of the loop
+        const bool fixed = (8 % ngr) == 0;
+        const int step = fixed ? 8 / ngr : 8;
+        int gr = fixed ? warp % ngr : 0, tt = fixed ? warp / ngr : warp;
+        int tr = tt / ntc, tc = tt - tr * ntc;
+        const int items = fixed ? ntiles : ntiles * ngr;
 #pragma unroll 1
-        for (int it = warp; it < items; it += 8) {
-            const int gr = it % ngr, tt = it / ngr;
-            const int th = 2 * (tt / ntc) + pr, tw = 2 * (tt % ntc) + pq;
+        for (; tt < items; tt += step) {
+            int th, tw;
+            if (fixed) {
+                th = 2 * tr + pr; tw = 2 * tc + pq;
+                tc += step;
+                while (tc >= ntc) { tc -= ntc; ++tr; }
+            } else {
+                gr = tt % ngr;
+                const int t2 = tt / ngr;
+                th = 2 * (t2 / ntc) + pr; tw = 2 * (t2 % ntc) + pq;
+            }
             const int cl = gr * 32 + lane;
             if (cl < nch) {
-                const long long base = (((long long)b * nH + th) * nW + tw) * C + c0 + cl;
+                const float *gp = dV + ((((long long)b * nH + th) * nW + tw) * C + c0 + cl);
+                const float *vp = MASK ? Vm + ((((long long)b * nH + th) * nW + tw) * C + c0 + cl) : nullptr;
                 float g[4][4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) g[i][j] = __ldg(dV + (long long)(4 * i + j) * plane + base);
+                for (int t = 0; t < 16; ++t) g[t >> 2][t & 3] = __ldg(gp + (long long)t * plane);
                 if (MASK) {
+                    float v[16];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int t = 0; t < 16; ++t) v[t] = __ldg(vp + (long long)t * plane);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if (!(__ldg(Vm + (long long)(4 * i + j) * plane + base) > 0.f)) g[i][j] = 0.f;
+                    for (int t = 0; t < 16; ++t)
+                        if (!(v[t] > 0.f)) g[t >> 2][t & 3] = 0.f;
                 }
                 // d = B g B^T, B[y][i] = Bt[i][y]: along one axis (u0..u3) -> (u0, u1 - u2 + u3, -u0 + u1 + u2, -u3)
                 float r[4][4];
