@@ -505,7 +505,7 @@ def sub_resnet(ctx, args, steps, total=256):
                "image": 224, "stage5_spatial": 14 if args.stage5_at_14 else 7, "layout": args.net_layout, "dtype": "tf32" if args.math == "tf32" else "f32",
                "launch": "eager" if graphs is None else "one CUDA graph per input buffer, replayed",
                "winograd_tflops_dense": model.winograd_flops(total) / (ms * 1e-3) / 1e12,
-               "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; max-pools on this library's kernel; stem, 1x1 shortcuts, FC on stock torch"}
+               "winograd_layers": "16, densities 0.6/0.4/0.3/0.2 by stage; 7x7 stem + pool1 and the max-pools on this library's kernels; 1x1 shortcuts, FC on stock torch"}
         if ctx.world > 1:      # the one collective of the sharded forward: every rank receives all logits (not on the timed path above)
             gm = timed(ctx, lambda i: wg2x2.shard.gather_batch(last["y"], total), 10, warmup=2)
             full = wg2x2.shard.gather_batch(last["y"], total)

@@ -227,6 +227,20 @@ int wg2x2_maxpool3x3s2_same_nhwc_in(const float *X, float *Y, float *Y_relu, con
                                     const float *relu_shift, int B, int C, int H, int W, void *stream);
 
 /*
+ * The dense head of the reference's ResNet-18-var graph as one kernel: Conv2D('conv1', image, 64, 7, stride=2) (no
+ * bias, no activation) followed by MaxPooling('pool1', l, 3, stride=2, padding='SAME'), both with TensorFlow's SAME
+ * padding (ResNet-18-var/imagenet-resnet-transWino-prune.py:112-114).  X (B,3,H,W) NCHW with H and W multiples of 4 and
+ * W <= 224; Y (B,64,H/4,W/4) NCHW; Y_relu as in wg2x2_maxpool3x3s2_same.  The convolution runs on the tensor cores
+ * with TF32 operands and FP32 accumulation and its (B,64,H/2,W/2) result never reaches memory.  Other sizes return
+ * WG2X2_ERR_UNSUPPORTED (run a stock convolution and wg2x2_maxpool3x3s2_same instead).
+ * wg2x2_stem_prepare arranges the (64,3,7,7) weights once into wg2x2_stem_prepared_floats() floats for the kernel.
+ */
+int wg2x2_stem_prepared_floats(void);
+int wg2x2_stem_prepare(const float *W, float *Wp, void *stream);
+int wg2x2_stem7x7s2_pool(const float *X, const float *Wp, float *Y, float *Y_relu, const float *relu_scale,
+                         const float *relu_shift, int B, int H, int W, void *stream);
+
+/*
  * Status word of the most recent kernel on this device that uses bounded waits
  * (the tcgen05 path): 0, or WG2X2_ERR_TIMEOUT with a code saying where it gave up.
  * Synchronises the given stream.

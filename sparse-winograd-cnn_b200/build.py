@@ -8,7 +8,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["imtrans.cu", "conv_ffma.cu", "conv_tc.cu", "api.cu", "ref_launchers.cu", "noalloc.cu", "pool.cu"]
+SOURCES = ["imtrans.cu", "conv_ffma.cu", "conv_tc.cu", "api.cu", "ref_launchers.cu", "noalloc.cu", "pool.cu", "stem.cu"]
 LIB = os.path.join(HERE, "libwinograd2x2_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -182,7 +182,15 @@ class ResNet18Var(torch.nn.Module):
         # the pools between the stages: this library's kernel on NCHW activations (it also hands out relu(pooled), which
         # the next stage's shortcut branch starts from), torch's elsewhere
         own_pool = not reference and self.layout == "NCHW" and image.is_cuda
-        if (self.layout == "NHWC" or own_pool) and not reference:
+        own_stem = own_pool and self.math == "tf32" and wg2x2.stem_supported(image.shape[2], image.shape[3])
+        pre = self.blocks[0][0]["pre"]
+        l_relu = None
+        if own_stem:      # conv1 + pool1 (+ the first shortcut's BNReLU) as one tensor-core kernel
+            if getattr(self, "_stem_prep", None) is None or self._stem_prep.device != image.device:
+                self._stem_prep = wg2x2.stem_prepare(stem.detach().contiguous())
+            l, l_relu = wg2x2.stem7x7s2_pool(image.contiguous(), self._stem_prep, with_relu=True,
+                                             relu_scale=pre.scale, relu_shift=pre.shift)
+        elif (self.layout == "NHWC" or own_pool) and not reference:
             # the stem runs channels-last (cuDNN's faster form for it); for NCHW activations the first pool reads that
             # layout and writes NCHW.  7x7/2 with TensorFlow's SAME padding (2 before, 3 after), written straight
             # into a channels-last buffer
@@ -191,13 +199,12 @@ class ResNet18Var(torch.nn.Module):
             x[:, :, 2:2 + H_, 2:2 + W_].copy_(image)
             if getattr(self, "_stem_cl", None) is None or self._stem_cl.device != stem.device:
                 self._stem_cl = stem.detach().contiguous(memory_format=torch.channels_last)
-            stem = self._stem_cl
+            l = F.conv2d(x, self._stem_cl, stride=2)
         else:
-            x = F.pad(image, (2, 3, 2, 3))
-        l = F.conv2d(x, stem, stride=2)
-        l_relu = None
-        if own_pool:       # pool1, and relu(BN(pool1)) for the first stage's shortcut from the same pass
-            pre = self.blocks[0][0]["pre"]
+            l = F.conv2d(F.pad(image, (2, 3, 2, 3)), stem, stride=2)
+        if own_stem:
+            pass
+        elif own_pool:     # pool1, and relu(BN(pool1)) for the first stage's shortcut from the same pass
             l, l_relu = wg2x2.maxpool3x3s2_same(l, with_relu=True, relu_scale=pre.scale, relu_shift=pre.shift)
         else:
             l = _same_pool(l)

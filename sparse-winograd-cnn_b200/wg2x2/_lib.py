@@ -57,6 +57,9 @@ _SIGS = {
     "wg2x2_layer_fwd_fused_supported": (_i, [_i, _i, _i, _i, _i, _i]),
     "wg2x2_maxpool3x3s2_same_nhwc_in": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
     "wg2x2_maxpool3x3s2_same": (_i, [_p, _p, _p, _p, _p, _i, _i, _i, _i, _p]),
+    "wg2x2_stem_prepared_floats": (_i, []),
+    "wg2x2_stem_prepare": (_i, [_p, _p, _p]),
+    "wg2x2_stem7x7s2_pool": (_i, [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
     "wg2x2_last_device_status": (_i, [_p, ctypes.POINTER(ctypes.c_uint)]),
     "wg2x2_set_wait_limit": (_i, [ctypes.c_longlong]),
     "wg2x2_test_drop_load": (_i, [_i]),

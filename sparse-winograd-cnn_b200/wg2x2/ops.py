@@ -270,6 +270,41 @@ def maxpool3x3s2_same(x, with_relu=False, relu_scale=None, relu_shift=None):
     return (y, yr) if with_relu else y
 
 
+def stem_supported(H, W):
+    """Image sizes the fused 7x7/2 convolution + pool kernel takes: multiples of 4, at most 224 wide."""
+    return H >= 4 and W >= 4 and H % 4 == 0 and W % 4 == 0 and W <= 224
+
+
+def stem_prepare(w):
+    """(64,3,7,7) stem weights -> the arrangement stem7x7s2_pool reads (TF32-rounded, in fragment order)."""
+    _chk(w, "w")
+    if tuple(w.shape) != (64, 3, 7, 7):
+        raise ValueError("stem weights must have shape (64,3,7,7), got %s" % (tuple(w.shape),))
+    wp = torch.empty(lib.wg2x2_stem_prepared_floats(), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.check(lib.wg2x2_stem_prepare(_ptr(w), _ptr(wp), _stream()), "wg2x2_stem_prepare")
+    return wp
+
+
+def stem7x7s2_pool(x, prepared, with_relu=False, relu_scale=None, relu_shift=None):
+    """pool1(conv1(x)) of the ResNet-18-var graph in one kernel: x (B,3,H,W) -> (B,64,H/4,W/4); with_relu=True also
+    returns relu(relu_scale[c] * pooled + relu_shift[c]).  `prepared` comes from stem_prepare."""
+    _chk(x, "x")
+    B, C, H, W = x.shape
+    if C != 3:
+        raise ValueError("stem input must have 3 channels, got %d" % C)
+    if not stem_supported(H, W):
+        raise ValueError("stem kernel needs H and W multiples of 4 and W <= 224, got %dx%d" % (H, W))
+    _chk_shape(prepared, (lib.wg2x2_stem_prepared_floats(),), "prepared")
+    _chk_shape(relu_scale, (64,), "relu_scale"); _chk_shape(relu_shift, (64,), "relu_shift")
+    y = torch.empty((B, 64, H // 4, W // 4), dtype=torch.float32, device=x.device)
+    yr = torch.empty_like(y) if with_relu else None
+    with torch.cuda.device(x.device):
+        _lib.check(lib.wg2x2_stem7x7s2_pool(_ptr(x), _ptr(prepared), _ptr(y), _ptr(yr), _ptr(relu_scale), _ptr(relu_shift),
+                                            B, H, W, _stream()), "wg2x2_stem7x7s2_pool")
+    return (y, yr) if with_relu else y
+
+
 def last_device_status():
     """(status, where) of the bounded device-side waits since the last reading; synchronises the current stream.
     The tensor-core calls above do not read it themselves (that would cost a synchronisation per call): after a

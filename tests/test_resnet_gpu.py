@@ -2,6 +2,7 @@
 the layers computed from the transform matrices in float64 (torch einsum)."""
 import pytest
 import torch
+import torch.nn.functional as F
 
 pytestmark = pytest.mark.gpu
 
@@ -85,3 +86,49 @@ def test_pool_kernel_matches_torch(shape):
     assert got4.is_contiguous() and torch.equal(got4, want)
     assert float((bnrelu4 - ref).abs().max()) <= 1e-6 * max(1.0, float(ref.abs().max()))
     assert torch.equal(wg2x2.maxpool3x3s2_same(xcl), want)
+
+
+def _tf32(x):
+    """Round to TF32, nearest with ties away from zero (cvt.rna.tf32.f32)."""
+    return ((x.contiguous().view(torch.int32) + 0x1000) & ~0x1FFF).view(torch.float32)
+
+
+@pytest.mark.parametrize("shape", [(2, 224, 224), (3, 64, 48), (1, 32, 224), (5, 100, 36), (1, 4, 4), (2, 8, 12), (37, 56, 56)])
+def test_stem_kernel_matches_dense_conv_and_pool(shape):
+    """wg2x2_stem7x7s2_pool (7x7/2 SAME convolution of a 3-channel image into 64 channels + 3x3/2 SAME max-pool in one
+    tensor-core kernel) against float64 convolution of the TF32-rounded operands followed by the torch pooling: only
+    the FP32 accumulation order differs, so 2e-5 of the largest value; the BNReLU output to the same bound."""
+    import wg2x2
+    from resnet18_var import _same_pool
+    B, H, W = shape
+    g = torch.Generator(device="cuda").manual_seed(B + H + W)
+    x = torch.randn((B, 3, H, W), device="cuda", generator=g)
+    w = torch.randn((64, 3, 7, 7), device="cuda", generator=g) * 0.1
+    sc = 1 + 0.2 * torch.randn(64, device="cuda", generator=g)
+    sh = 0.3 * torch.randn(64, device="cuda", generator=g)
+    assert wg2x2.stem_supported(H, W)
+    prep = wg2x2.stem_prepare(w)
+    conv = F.conv2d(F.pad(_tf32(x).double(), (2, 3, 2, 3)), _tf32(w).double(), stride=2)
+    want = _same_pool(conv.float())
+    got, bnrelu = wg2x2.stem7x7s2_pool(x, prep, with_relu=True, relu_scale=sc, relu_shift=sh)
+    tol = 2e-5 * float(want.abs().max())
+    assert got.shape == want.shape and float((got - want).abs().max()) <= tol
+    ref = torch.relu(want * sc.view(1, -1, 1, 1) + sh.view(1, -1, 1, 1))
+    assert float((bnrelu - ref).abs().max()) <= 2 * tol
+    assert torch.equal(wg2x2.stem7x7s2_pool(x, prep), got)
+    # against the plain FP32 convolution: TF32 operand rounding, 2e-3 of the largest value
+    keep = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        plain = _same_pool(F.conv2d(F.pad(x, (2, 3, 2, 3)), w, stride=2))
+    finally:
+        torch.backends.cudnn.allow_tf32 = keep
+    assert float((got - plain).abs().max()) <= 2e-3 * float(plain.abs().max())
+
+
+def test_stem_kernel_rejects_other_sizes():
+    import wg2x2
+    assert not wg2x2.stem_supported(226, 224) and not wg2x2.stem_supported(224, 228) and not wg2x2.stem_supported(224, 256)
+    x = torch.zeros((1, 3, 30, 32), device="cuda")
+    with pytest.raises(ValueError):
+        wg2x2.stem7x7s2_pool(x, wg2x2.stem_prepare(torch.zeros((64, 3, 7, 7), device="cuda")))
