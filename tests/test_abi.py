@@ -84,6 +84,15 @@ def test_misaligned_operands_are_refused_before_any_launch(lib):
     for bad in range(6):   # V, prepared, Y, out_scale, out_shift, residual
         ptrs = [off if i == bad else ok for i in range(6)]
         assert fwd(ptrs[0], ptrs[1], ptrs[2], B, 4, 4, C, K, 8, 8, 0, ptrs[3], ptrs[4], ptrs[5], ws, 1 << 40, None) == -1, bad
+    # the stem kernel copies the image in 16-byte pieces; sizes it does not take are UNSUPPORTED (-5), not a launch
+    stem = lib.wg2x2_stem7x7s2_pool
+    stem.argtypes = [P] * 6 + [ctypes.c_int] * 3 + [P]
+    assert stem(off, ok, ok, None, None, None, 2, 224, 224, None) == -1
+    assert stem(ok, off, ok, None, None, None, 2, 224, 224, None) == -1
+    assert stem(ok, ok, ok, None, ok, ok, 2, 224, 224, None) == -1          # an affine ReLU output without its tensor
+    for h, w in ((226, 224), (224, 222), (224, 228), (2, 224)):
+        assert stem(ok, ok, ok, None, None, None, 2, h, w, None) == -5, (h, w)
+    assert lib.wg2x2_stem_prepared_floats() == 21 * 32 * 16
 
 
 def test_wait_limit_argument(lib):
