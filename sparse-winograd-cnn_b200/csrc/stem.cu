@@ -13,9 +13,10 @@
 //     zero rows and columns standing for the padding), and A fragments are read straight from that staging with a
 //     per-k offset table: no im2col buffer exists anywhere;
 //   * warp w owns output columns 16w .. 16w+15 of both rows for all 64 channels (2 x 8 accumulator tiles), so the
-//     vertical maximum of a pool window is taken between its own registers (the row shared with the previous step
-//     is carried in registers too), and the horizontal one needs one value per output from the neighbouring
-//     column pair, exchanged through shared memory;
+//     vertical maximum of a pool window is taken between its own registers; the row shared with the previous step
+//     is parked in tensor memory meanwhile (tcgen05.st / tcgen05.ld of the 32 accumulator registers, 64 columns per
+//     block: registers are what limits the MMA loop, and tensor memory is otherwise idle here), and the horizontal
+//     maximum needs one value per output from the neighbouring column pair, exchanged through shared memory;
 //   * the weights are pre-rounded to TF32 and pre-arranged so that a lane fetches its sixteen B values of a k-step
 //     with four 16-byte loads.
 // K runs over the 21 (ky, channel) pairs times 8: the seven taps of a kernel row and a zero weight, so that every
@@ -45,7 +46,35 @@ struct StemSmem {
     float in[2][kStemBuf];
     float e[64 * kStemEPitch];
     float2 affine[64];                   // scale and shift of the ReLU output per channel
+    uint32_t tmem_base;                  // written by tcgen05.alloc
 };
+
+constexpr uint32_t kStemTmemCols = 64;   // warps 0..3 park their row in columns 0..31 of their 32 lanes, warps 4..6 in 32..63
+
+__device__ __forceinline__ void stem_tmem_st32(uint32_t taddr, const float (&r)[8][4])
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     ::"r"(taddr + 8 * q), "r"(__float_as_uint(r[2 * q][0])), "r"(__float_as_uint(r[2 * q][1])),
+                       "r"(__float_as_uint(r[2 * q][2])), "r"(__float_as_uint(r[2 * q][3])), "r"(__float_as_uint(r[2 * q + 1][0])),
+                       "r"(__float_as_uint(r[2 * q + 1][1])), "r"(__float_as_uint(r[2 * q + 1][2])), "r"(__float_as_uint(r[2 * q + 1][3]))
+                     : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void stem_tmem_ld32(uint32_t taddr, float (&r)[8][4])
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint32_t u[8];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7])
+                     : "r"(taddr + 8 * q) : "memory");
+#pragma unroll
+        for (int e = 0; e < 8; ++e) r[2 * q + (e >> 2)][e & 3] = __uint_as_float(u[e]);
+    }
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
 
 // (64,3,7,7) weights -> [k-step][4][lane][4]: a lane's sixteen values e = 4*quad + comp are B fragment register 0
 // (k = 8*ks + t) of the eight 8-channel tiles for e < 8, register 1 (k = 8*ks + t + 4) for e >= 8, channel
@@ -157,7 +186,16 @@ stem_pool_kernel(const float *__restrict__ X, const float *__restrict__ Wp, floa
     for (int i = tid; i < 2 * kStemBuf / 4; i += kStemThreads) reinterpret_cast<float4 *>(&sm.in[0][0])[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = tid; i < kStemWt / 4; i += kStemThreads) reinterpret_cast<float4 *>(sm.wt)[i] = __ldg(reinterpret_cast<const float4 *>(Wp) + i);
     if (tid < 64) sm.affine[tid] = rs ? make_float2(__ldg(rs + tid), __ldg(rb + tid)) : make_float2(1.f, 0.f);
+    if (warp == 0) {     // two blocks of this kernel share an SM's 512 columns: the allocation never has to wait
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"((uint32_t)__cvta_generic_to_shared(&sm.tmem_base)), "r"(kStemTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // a warp reaches the 32 tensor-memory lanes of its quarter (warp % 4) only
+    const uint32_t tcarry = sm.tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * 32);
 
     const int nsteps = pr1 - pr0 + 1;                  // step 0 computes convolution row 2*pr0 alone
     stem_stage(sm.in[0], img, 2 * pr0 - 1, H, W, lane, warp);
@@ -165,12 +203,6 @@ stem_pool_kernel(const float *__restrict__ X, const float *__restrict__ Wp, floa
     const int g = lane >> 2, t = lane & 3;
     const int j = 8 * warp + g;                        // pooled column of this lane
     const bool col_ok = j < PW;
-    float carry[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) carry[nt][e] = 0.f;
-
     for (int s = 0; s < nsteps; ++s) {
         const int i = pr0 + s - 1;                     // pooled row this step completes (s >= 1)
         if (s + 1 < nsteps) {
@@ -189,13 +221,13 @@ stem_pool_kernel(const float *__restrict__ X, const float *__restrict__ Wp, floa
                 for (int e = 0; e < 4; ++e) acc[m][nt][e] = 0.f;
         if (s == 0) {
             stem_rows<false>(sm.in[0], reinterpret_cast<const float4 *>(sm.wt), lane, warp, acc);
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) carry[nt][e] = acc[1][nt][e];
+            stem_tmem_st32(tcarry, acc[1]);
         } else {
             stem_rows<true>(sm.in[s & 1], reinterpret_cast<const float4 *>(sm.wt), lane, warp, acc);
             const bool low_ok = 2 * i + 2 < OH;        // the window's third row exists
+            float carry[8][4];                         // convolution row 2*i, computed by the previous step
+            stem_tmem_ld32(tcarry, carry);
+            stem_tmem_st32(tcarry, acc[1]);
             float h[8][2];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) {
@@ -204,7 +236,6 @@ stem_pool_kernel(const float *__restrict__ X, const float *__restrict__ Wp, floa
                 for (int e = 0; e < 4; ++e) {
                     v[e] = fmaxf(carry[nt][e], acc[0][nt][e]);
                     if (low_ok) v[e] = fmaxf(v[e], acc[1][nt][e]);
-                    carry[nt][e] = acc[1][nt][e];
                 }
                 h[nt][0] = fmaxf(v[0], v[2]);
                 h[nt][1] = fmaxf(v[1], v[3]);
@@ -235,6 +266,12 @@ stem_pool_kernel(const float *__restrict__ X, const float *__restrict__ Wp, floa
             }
         }
         __syncthreads();   // the buffer just read is staged into at the top of the next step; e[] is rewritten
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(kStemTmemCols) : "memory");
     }
 }
 
