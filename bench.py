@@ -385,6 +385,31 @@ class LayerFwd:
         return roof, which
 
 
+def library_tf32(ctx, shapes, n=12):
+    """Calibration, not a product path: cuBLAS TF32 batched GEMMs (torch.bmm, allow_tf32) on the given (batch, M, K, N)
+    products with resident operands and nothing else (no transforms, masks or epilogues) -- what the vendor library reaches
+    on the same tensor-core shapes, beside the measured bf16 / 2 roof."""
+    torch = ctx.torch
+    keep = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        ops = [(torch.randn((b, m, k), device=ctx.dev), torch.randn((b, k, nn), device=ctx.dev)) for (b, m, k, nn) in shapes]
+        outs = [torch.empty((b, m, nn), device=ctx.dev) for (b, m, k, nn) in shapes]
+
+        def run(i):
+            for (a, w), o in zip(ops, outs):
+                torch.bmm(a, w, out=o)
+
+        for i in range(3):
+            run(i)
+        ms = each_launch_ms(torch, run, n)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = keep
+    flops = sum(2.0 * b * m * k * nn for (b, m, k, nn) in shapes)
+    return {"what": "cuBLAS TF32 (torch.bmm) on the same products, operands resident, nothing else", "shapes_b_m_k_n": [list(x) for x in shapes],
+            "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+
+
 def sub_layer_fwd(ctx, name, args, steps):
     """configs.<name>: one layer forward workload, device-resident."""
     wl = dict(WORKLOADS[name])
@@ -406,6 +431,9 @@ def sub_layer_fwd(ctx, name, args, steps):
         w2 = (0.05 * np.random.default_rng(2).standard_normal((16, wl["C"], wl["K"]))).astype(np.float32)
         rec["skip_rate_magnitude_mask"] = zero_block_fraction(gen_prune_mask(w2, wl["density"]))   # the reference's top-|w| mask, same density
         rec["skip_note"] = "unstructured masks leave no 64 x 32 block empty: tensor-pipe figures are from dense flops"
+    if not L.use_fused and wl["C"] >= 256:       # tensor-bound shape: the vendor library's rate on the same 16 products, for scale
+        P = wl["B"] * ((wl["H"] + 1) // 2) * ((wl["W"] + 1) // 2)
+        rec["library_tf32"] = library_tf32(ctx, [(16, P, wl["C"], wl["K"])])
     del L
     ctx.torch.cuda.empty_cache()
     return rec
@@ -459,6 +487,8 @@ def sub_backward(ctx, args, steps, math="tf32", batch=0):
                         "imtrans_bwd_gbs": (64.0 * P * C + 4.0 * B * C * H * W) / (ms_g * 1e-3) / 1e9}}
     del X, V, dYs, hold
     torch.cuda.empty_cache()
+    if math == "tf32":     # the vendor library's rate on the two gradient products (dV = dM.W^T, dW = V^T.dM), for scale
+        rec["library_tf32"] = library_tf32(ctx, [(16, P, K, C), (16, C, P, K)])
     return rec
 
 
@@ -816,7 +846,7 @@ def main():
     try:
         if args.workload == "cfg4":
             run_single(args, ctx, lambda: sub_resnet(ctx, args, max(3, min(args.steps, 30)), total=args.batch or 256),
-                       "resnet18_var_forward_throughput", "strong", 32)
+                       "resnet18_var_forward_throughput", "strong", 35)
         elif args.workload == "cfg5":
             run_single(args, ctx, lambda: sub_backward(ctx, args, max(3, min(args.steps, 200)), math=args.bwd_math, batch=args.batch),
                        "winograd_relu_conv_layer_bwd_throughput", "weak", 6)
