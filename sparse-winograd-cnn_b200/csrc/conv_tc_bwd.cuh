@@ -606,16 +606,68 @@ static bool make_map_out(CUtensorMap *map, float *ptr, long long cols, long long
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+#include "conv_tc_gemm2.cuh"
+
+// How many pairs of SMs can hold a pair of CTAs of the cta_group::2 kernel at once (0: this device cannot, or
+// WG2X2_GEMM_PAIR=0 in the environment); asked once per device and kernel.
 template <int KIND>
-static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, GgParams &prm, cudaStream_t st)
+static int gg_pair_clusters()
 {
-    if (cudaFuncSetAttribute(conv_grad_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgSmemBytes) != cudaSuccess)
-        return WG2X2_ERR_LAUNCH;
+    static std::atomic<int> cached[64];
+    static std::atomic<int> init{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (!init.load()) {
+        for (auto &c : cached) c.store(-1);
+        init.store(1);
+    }
+    int n = cached[dev].load();
+    if (n >= 0) return n;
+    const char *env = getenv("WG2X2_GEMM_PAIR");
+    n = 0;
+    if (!(env && env[0] == '0') &&
+        cudaFuncSetAttribute(conv_grad_gemm_tc2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGg2SmemBytes) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * kNumSMs);
+        cfg.blockDim = dim3(kTcThreads);
+        cfg.dynamicSmemBytes = kGg2SmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int got = 0;
+        if (cudaOccupancyMaxActiveClusters(&got, conv_grad_gemm_tc2_kernel<KIND>, &cfg) == cudaSuccess && got > 0) n = got;
+        else (void)cudaGetLastError();
+    }
+    cached[dev].store(n);
+    return n;
+}
+
+// mapB_half (KIND 1): the B operand with boxes of N/2 rows, for the kernel on pairs of SMs; NULL keeps the one-CTA kernel.
+template <int KIND>
+static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, GgParams &prm, cudaStream_t st, const CUtensorMap *mapB_half = nullptr)
+{
     // results without a mask leave by TMA store where the output can be described to TMA (else: the load/store path)
     CUtensorMap mapOut = mapA;
     const bool needs_mask = prm.mask && (KIND == 1 || prm.direct);
     prm.tma_out = (!needs_mask && prm.cols >= 32 &&
                    make_map_out(&mapOut, prm.out, prm.cols, prm.rows, 16LL * (prm.direct ? 1 : prm.splits))) ? 1 : 0;
+    // Two SMs per 256 x N tile where that measured faster: long contractions (dW always contracts over all tiles; the
+    // products with 512 or more channels), whose pipeline outlasts the pair's extra hand-shakes, and no mask to fetch in
+    // the epilogue.  Short contractions (256 channels) and dV with its ReLU mask are HBM-bound and stay on one CTA.
+    const bool pair_pays = KIND == 0 ? prm.contr >= 1024 : (mapB_half && prm.contr >= 512 && !needs_mask);
+    const int nclusters = (prm.nRB >= 2 && prm.N >= 128 && pair_pays) ? gg_pair_clusters<KIND>() : 0;
+    if (nclusters > 0) {
+        GgParams p2 = prm;
+        p2.nRB = cdiv(prm.nRB, 2);
+        p2.units = prm.units / prm.nRB * p2.nRB;
+        const int pairs = p2.units < nclusters ? p2.units : nclusters;
+        conv_grad_gemm_tc2_kernel<KIND><<<2 * pairs, kTcThreads, kGg2SmemBytes, st>>>(mapA, KIND == 1 ? *mapB_half : mapB, mapOut, p2);
+        return launch_status();
+    }
+    if (cudaFuncSetAttribute(conv_grad_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgSmemBytes) != cudaSuccess)
+        return WG2X2_ERR_LAUNCH;
     const int grid = prm.units < kNumSMs ? prm.units : kNumSMs;
     conv_grad_gemm_tc_kernel<KIND><<<grid, kTcThreads, kGgSmemBytes, st>>>(mapA, mapB, mapOut, prm);
     return launch_status();
@@ -665,9 +717,11 @@ int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, unsi
     prm.out = dV;
     prm.mask = relu ? V : nullptr;
     prm.block_map = map; prm.map_mode = 2; prm.map_nkb = nKB;
-    CUtensorMap mapA, mapB;
-    if (!make_map_gg(&mapA, dM, K, P, false, 128) || !make_map_gg(&mapB, Wr, K, C, false, prm.N)) return WG2X2_ERR_LAUNCH;
-    return gg_launch<1>(mapA, mapB, prm, st);
+    CUtensorMap mapA, mapB, mapBh;
+    if (!make_map_gg(&mapA, dM, K, P, false, 128) || !make_map_gg(&mapB, Wr, K, C, false, prm.N) ||
+        !make_map_gg(&mapBh, Wr, K, C, false, prm.N / 2))
+        return WG2X2_ERR_LAUNCH;
+    return gg_launch<1>(mapA, mapB, prm, st, &mapBh);
 }
 
 size_t conv_bwd_tc_workspace_bytes(long long P, int C, int K, int want_dW)
@@ -837,10 +891,11 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
     prm.block_map = reinterpret_cast<const unsigned long long *>(static_cast<const unsigned char *>(prepared) +
                                                                  align_up((size_t)16 * K * C * sizeof(float), 256));
     prm.map_mode = 1; prm.map_nkb = cdiv(K, kBlockN);
-    CUtensorMap mapA, mapB;
-    if (!make_map_gg(&mapA, V, C, P, false, 128) || !make_map_gg(&mapB, static_cast<const float *>(prepared), C, K, false, prm.N))
+    CUtensorMap mapA, mapB, mapBh;
+    if (!make_map_gg(&mapA, V, C, P, false, 128) || !make_map_gg(&mapB, static_cast<const float *>(prepared), C, K, false, prm.N) ||
+        !make_map_gg(&mapBh, static_cast<const float *>(prepared), C, K, false, prm.N / 2))
         return WG2X2_ERR_LAUNCH;
-    int s = gg_launch<1>(mapA, mapB, prm, st);
+    int s = gg_launch<1>(mapA, mapB, prm, st, &mapBh);
     if (s != WG2X2_OK) return s;
     OutExtras ex{out_scale, out_shift, residual};
     if (layout == WG2X2_NHWC) {
