@@ -423,3 +423,41 @@ def test_wide_forward_path(wg, oracle, shape, layout):
     Yc = wg.conv_fwd(_dev(V), _dev(Wt), H, W, layout=layout, math="tf32").cpu().numpy()      # raw-weight entry point
     assert oracle.max_rel(fix(Yc), want) <= TOL_TF32
     _status_ok(wg)
+
+
+_PAIR_CHILD = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import wg2x2
+g = torch.Generator().manual_seed(7)
+B, C, K, H, W = 70, 512, 512, 7, 7          # P = 1120 tiles: nine row blocks, the last pair half empty; contraction 1120 / 512
+X = torch.randn((B, C, H, W), generator=g).cuda()
+Wt = (0.05 * torch.randn((16, C, K), generator=g)).cuda()
+dY = torch.randn((B, K, H, W), generator=g).cuda()
+V = wg2x2.imtrans_fwd(X, relu=True, layout="NCHW")
+dV, dW = wg2x2.conv_bwd(V, Wt, dY, layout="NCHW", relu=False, math="tf32")
+Y = wg2x2.conv_fwd_prepared(V, wg2x2.prepare_weights(Wt), K, H, W, layout="NCHW")
+st, where = wg2x2.last_device_status()
+assert st == 0, hex(where)
+np.savez(sys.argv[2], dV=dV.cpu().numpy(), dW=dW.cpu().numpy(), Y=Y.cpu().numpy())
+"""
+
+
+def test_pair_of_sms_kernel_equals_the_one_cta_kernel(tmp_path):
+    """The GEMM on pairs of SMs (tcgen05 cta_group::2: dW, and products over 512 channels) against the one-CTA kernel
+    (WG2X2_GEMM_PAIR=0) on the same inputs, each in its own process: every output element is the same sum in the same
+    order, so the results are equal bit for bit.  Nine row blocks: the last pair works with one CTA's rows out of range."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "sparse-winograd-cnn_b200")
+    outs = []
+    for flag in ("1", "0"):
+        path = str(tmp_path / ("pair%s.npz" % flag))
+        env = dict(os.environ, WG2X2_GEMM_PAIR=flag)
+        r = subprocess.run([sys.executable, "-c", _PAIR_CHILD, root, path], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(np.load(path))
+    for key in ("dV", "dW", "Y"):
+        assert np.array_equal(outs[0][key], outs[1][key]), key
+    assert np.isfinite(outs[0]["dW"]).all() and float(np.abs(outs[0]["dW"]).max()) > 0
