@@ -166,13 +166,28 @@ __global__ void __launch_bounds__(256) round_and_map_kernel(const float *__restr
 {
     const int kb = blockIdx.x, cc = blockIdx.y, t = blockIdx.z;
     int nz = 0;
-    for (int e = threadIdx.x; e < 32 * 64; e += 256) {
-        const int c = cc * 32 + (e >> 6), k = kb * 64 + (e & 63);
-        if (c < C && k < K) {
-            const long long o = ((long long)t * C + c) * K + k;
-            const float w = round_tf32(__ldg(Wt + o));
-            Wr[o] = w;
-            nz |= (w != 0.f);
+    if ((K & 3) == 0 && ((reinterpret_cast<uintptr_t>(Wt) | reinterpret_cast<uintptr_t>(Wr)) & 15u) == 0) {
+        // 16 bytes per access: 32 rows of 16 float4, two per thread
+#pragma unroll
+        for (int e = threadIdx.x; e < 32 * 16; e += 256) {
+            const int c = cc * 32 + (e >> 4), k = kb * 64 + 4 * (e & 15);
+            if (c < C && k < K) {
+                const long long o = ((long long)t * C + c) * K + k;
+                float4 w = __ldg(reinterpret_cast<const float4 *>(Wt + o));
+                w.x = round_tf32(w.x); w.y = round_tf32(w.y); w.z = round_tf32(w.z); w.w = round_tf32(w.w);
+                *reinterpret_cast<float4 *>(Wr + o) = w;
+                nz |= (w.x != 0.f) | (w.y != 0.f) | (w.z != 0.f) | (w.w != 0.f);
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < 32 * 64; e += 256) {
+            const int c = cc * 32 + (e >> 6), k = kb * 64 + (e & 63);
+            if (c < C && k < K) {
+                const long long o = ((long long)t * C + c) * K + k;
+                const float w = round_tf32(__ldg(Wt + o));
+                Wr[o] = w;
+                nz |= (w != 0.f);
+            }
         }
     }
     nz = __syncthreads_or(nz);
