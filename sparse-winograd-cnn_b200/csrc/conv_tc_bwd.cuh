@@ -295,6 +295,7 @@ struct GgParams {
     const unsigned long long *block_map;
     int map_mode, map_nkb;
     int tma_out;             // results that need no mask leave by TMA store (mapOut) straight from the staging block
+    int mn4;                 // KIND 0: the operand maps are 4-D (channel blocks of 32 as a dimension of their own): one TMA load per operand and chunk
 };
 
 // Bit n of the result is set when contraction chunk n (32 elements) of this unit has to run: the first chunk always
@@ -332,6 +333,13 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr)
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)1 << 61;
     return d;
+}
+
+__device__ __forceinline__ void tma_load_4d_gg(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // shared memory -> global, clipped to the tensor; completion is tracked by the thread's bulk async-groups
@@ -404,7 +412,10 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                     mbar_expect_tx(full_bar(s), stage_tx);
                     const uint32_t a_dst = base + s * kGgStageBytes;
                     const uint32_t b_dst = a_dst + kGgABytes;
-                    if (KIND == 0) {
+                    if (KIND == 0 && prm.mn4) {      // all 32-channel blocks of an operand in one box each
+                        tma_load_4d_gg(a_dst, &mapA, full_bar(s), 0, (int)kc, rb * 4, t);
+                        tma_load_4d_gg(b_dst, &mapB, full_bar(s), 0, (int)kc, cb * (N / 32), t);
+                    } else if (KIND == 0) {
 #pragma unroll
                         for (int mb = 0; mb < 4; ++mb)
                             tma_load_3d(a_dst + mb * kGgBoxBytes, &mapA, full_bar(s), rb * 128 + mb * 32, (int)kc, t);
@@ -590,6 +601,22 @@ static bool make_map_gg(CUtensorMap *map, const float *ptr, long long ch, long l
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// MN-major operand with the 32-channel blocks as a dimension of their own: (32, rows, ch / 32, 16), box = 32 x 32 rows x
+// nblk blocks, which lands in shared memory as nblk consecutive 4 KB blocks -- the layout the MN-major descriptor reads --
+// from ONE load instead of nblk.  Needs ch % 32 == 0.
+static bool make_map_gg4(CUtensorMap *map, const float *ptr, long long ch, long long rows, int nblk)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || (ch & 31) || nblk < 1 || nblk > 8) return false;
+    cuuint64_t dims[4] = {32, (cuuint64_t)rows, (cuuint64_t)(ch / 32), 16};
+    cuuint64_t strides[3] = {(cuuint64_t)ch * 4, 128, (cuuint64_t)rows * ch * 4};
+    cuuint32_t box[4] = {32, 32, (cuuint32_t)nblk, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int gg_cols(int n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
 // Splits of the P range for dW: enough units for every SM, at least 8 chunks of 32 tiles per split
@@ -659,7 +686,8 @@ static int gg_pair_clusters()
     return n;
 }
 
-// mapB_half (KIND 1): the B operand with boxes of N/2 rows, for the kernel on pairs of SMs; NULL keeps the one-CTA kernel.
+// mapB_half: the B operand with boxes of N/2 rows (KIND 1) or N/64 channel blocks (KIND 0, 4-D maps) for the kernel on pairs
+// of SMs; NULL: KIND 1 stays on one CTA, KIND 0 loads its 32 x 32 boxes one by one in either kernel.
 template <int KIND>
 static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, GgParams &prm, cudaStream_t st, const CUtensorMap *mapB_half = nullptr)
 {
@@ -678,7 +706,7 @@ static int gg_launch(const CUtensorMap &mapA, const CUtensorMap &mapB, GgParams 
         p2.nRB = cdiv(prm.nRB, 2);
         p2.units = prm.units / prm.nRB * p2.nRB;
         const int pairs = p2.units < nclusters ? p2.units : nclusters;
-        conv_grad_gemm_tc2_kernel<KIND><<<2 * pairs, kTcThreads, kGg2SmemBytes, st>>>(mapA, KIND == 1 ? *mapB_half : mapB, mapOut, p2);
+        conv_grad_gemm_tc2_kernel<KIND><<<2 * pairs, kTcThreads, kGg2SmemBytes, st>>>(mapA, mapB_half ? *mapB_half : mapB, mapOut, p2);
         return launch_status();
     }
     if (cudaFuncSetAttribute(conv_grad_gemm_tc_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGgSmemBytes) != cudaSuccess)
@@ -703,9 +731,16 @@ int conv_dw_tc(const float *V, const float *dM, const float *mask, float *dW, fl
     prm.out = prm.direct ? dW : partial;
     prm.mask = mask;
     prm.block_map = nullptr; prm.map_mode = 0; prm.map_nkb = 0;
-    CUtensorMap mapV, mapM;
-    if (!make_map_gg(&mapV, V, C, P, true, 32) || !make_map_gg(&mapM, dM, K, P, true, 32)) return WG2X2_ERR_LAUNCH;
-    const int s = gg_launch<0>(mapV, mapM, prm, st);
+    CUtensorMap mapV, mapM, mapMh;
+    prm.mn4 = (C % 32 == 0 && K % 32 == 0) ? 1 : 0;
+    if (prm.mn4) {
+        if (!make_map_gg4(&mapV, V, C, P, 4) || !make_map_gg4(&mapM, dM, K, P, prm.N / 32) ||
+            (prm.N >= 64 && !make_map_gg4(&mapMh, dM, K, P, prm.N / 64)))
+            return WG2X2_ERR_LAUNCH;
+    } else if (!make_map_gg(&mapV, V, C, P, true, 32) || !make_map_gg(&mapM, dM, K, P, true, 32)) {
+        return WG2X2_ERR_LAUNCH;
+    }
+    const int s = gg_launch<0>(mapV, mapM, prm, st, (prm.mn4 && prm.N >= 64) ? &mapMh : nullptr);
     if (s != WG2X2_OK) return s;
     if (!prm.direct) dw_reduce_launch(partial, mask, dW, (long long)16 * C * K, prm.splits, st);
     return launch_status();
@@ -731,7 +766,7 @@ int conv_dv_tc(const float *V, const float *Wt, const float *dM, float *Wr, unsi
     prm.direct = 1;
     prm.out = dV;
     prm.mask = relu ? V : nullptr;
-    prm.block_map = map; prm.map_mode = 2; prm.map_nkb = nKB;
+    prm.block_map = map; prm.map_mode = 2; prm.map_nkb = nKB; prm.mn4 = 0;
     CUtensorMap mapA, mapB, mapBh;
     if (!make_map_gg(&mapA, dM, K, P, false, 128) || !make_map_gg(&mapB, Wr, K, C, false, prm.N) ||
         !make_map_gg(&mapBh, Wr, K, C, false, prm.N / 2))
@@ -905,7 +940,7 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
     // the zero-block map that weights_prepare built behind the packed weights
     prm.block_map = reinterpret_cast<const unsigned long long *>(static_cast<const unsigned char *>(prepared) +
                                                                  align_up((size_t)16 * K * C * sizeof(float), 256));
-    prm.map_mode = 1; prm.map_nkb = cdiv(K, kBlockN);
+    prm.map_mode = 1; prm.map_nkb = cdiv(K, kBlockN); prm.mn4 = 0;
     CUtensorMap mapA, mapB, mapBh;
     if (!make_map_gg(&mapA, V, C, P, false, 128) || !make_map_gg(&mapB, static_cast<const float *>(prepared), C, K, false, prm.N) ||
         !make_map_gg(&mapBh, static_cast<const float *>(prepared), C, K, false, prm.N / 2))

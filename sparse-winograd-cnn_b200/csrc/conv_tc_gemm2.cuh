@@ -50,6 +50,12 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 // D[tmem of both CTAs] (+)= A * B, M = 256 (128 rows per CTA), K = 8 (tf32); issued by the leader only
 __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
@@ -138,12 +144,20 @@ conv_grad_gemm_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid
                 for (long long kc = kbeg; kc < kend; kc += 32) {
                     if (KIND == 1 && kc < 64 * 32 && !((live >> (kc >> 5)) & 1ull)) continue;   // all-zero weight blocks: nothing to add
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x500u | s)) { ok = false; break; }
+#ifdef WG_GG_KO_LOAD   // development knock-out: no operand loads (results wrong)
+                    if (rank == 0) mbar_arrive(full_bar(s));
+                    if (++s == kGg2Stages) { s = 0; ph ^= 1u; }
+                    continue;
+#endif
                     if (rank == 0) mbar_expect_tx(full_bar(s), stage_tx);
                     const uint32_t fbar = mapa_rank0(full_bar(s));
                     const uint32_t a_dst = base + s * kGg2StageBytes;
                     const uint32_t b_dst = a_dst + kGgABytes;
                     const int row0 = (2 * rb + (int)rank) * 128, col0 = cb * N + (int)rank * NH;
-                    if (KIND == 0) {
+                    if (KIND == 0 && prm.mn4) {      // all 32-channel blocks of an operand in one box each
+                        tma_load_4d_pair(a_dst, &mapA, fbar, 0, (int)kc, row0 / 32, t);
+                        tma_load_4d_pair(b_dst, &mapB, fbar, 0, (int)kc, col0 / 32, t);
+                    } else if (KIND == 0) {
 #pragma unroll
                         for (int mb = 0; mb < 4; ++mb)
                             tma_load_3d_pair(a_dst + mb * kGgBoxBytes, &mapA, fbar, row0 + mb * 32, (int)kc, t);
@@ -192,9 +206,11 @@ conv_grad_gemm_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid
                     const uint64_t bdesc = KIND == 0 ? make_desc_mn_sw128(a_addr + kGgABytes) : make_desc_k_sw128(a_addr + kGgABytes);
                     const uint32_t step = KIND == 0 ? 64u : 2u;   // 1024 B / 32 B per 8 contraction steps
                     if (leader) {
+#ifndef WG_GG_KO_MMA   // development knock-out: no MMAs (results wrong)
 #pragma unroll
                         for (int kg = 0; kg < 4; ++kg)
                             umma_tf32_pair(d_tmem, adesc + step * kg, bdesc + step * kg, idesc, (first && kg == 0) ? 0u : 1u);
+#endif
                         umma_commit_pair(empty_bar(s));
                     }
                     __syncwarp();
