@@ -144,11 +144,6 @@ conv_grad_gemm_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid
                 for (long long kc = kbeg; kc < kend; kc += 32) {
                     if (KIND == 1 && kc < 64 * 32 && !((live >> (kc >> 5)) & 1ull)) continue;   // all-zero weight blocks: nothing to add
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, 0x500u | s)) { ok = false; break; }
-#ifdef WG_GG_KO_LOAD   // development knock-out: no operand loads (results wrong)
-                    if (rank == 0) mbar_arrive(full_bar(s));
-                    if (++s == kGg2Stages) { s = 0; ph ^= 1u; }
-                    continue;
-#endif
                     if (rank == 0) mbar_expect_tx(full_bar(s), stage_tx);
                     const uint32_t fbar = mapa_rank0(full_bar(s));
                     const uint32_t a_dst = base + s * kGg2StageBytes;
@@ -206,11 +201,9 @@ conv_grad_gemm_tc2_kernel(const __grid_constant__ CUtensorMap mapA, const __grid
                     const uint64_t bdesc = KIND == 0 ? make_desc_mn_sw128(a_addr + kGgABytes) : make_desc_k_sw128(a_addr + kGgABytes);
                     const uint32_t step = KIND == 0 ? 64u : 2u;   // 1024 B / 32 B per 8 contraction steps
                     if (leader) {
-#ifndef WG_GG_KO_MMA   // development knock-out: no MMAs (results wrong)
 #pragma unroll
                         for (int kg = 0; kg < 4; ++kg)
                             umma_tf32_pair(d_tmem, adesc + step * kg, bdesc + step * kg, idesc, (first && kg == 0) ? 0u : 1u);
-#endif
                         umma_commit_pair(empty_bar(s));
                     }
                     __syncwarp();
