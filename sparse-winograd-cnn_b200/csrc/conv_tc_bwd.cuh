@@ -492,21 +492,30 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
             const long long row = (long long)rb * 128 + q * 32 + lane;
             const long long row_off = (prm.direct ? 0 : (long long)split * plane_elems) + ((long long)t * prm.rows + row) * prm.cols;
             const int ncol_half = N / 2;
+            // offsets of the 8 lines this lane will store in a 32-column block, and their mask values.  They are fetched one
+            // block ahead (the first block of a unit before the accumulator is even waited for), so that the memory latency
+            // of the mask hides behind the previous block's TMEM load, turn and stores instead of stalling every block.
+            long long off[8], off_nx[8];
+            float4 mk[8], mk_nx[8];
+            auto fetch = [&](int cc_f, long long (&o)[8], float4 (&m)[8]) {
+                const int col_f = cb * N + half * ncol_half + cc_f;
+                const long long my_f = (row < prm.rows && col_f < prm.cols) ? row_off + col_f : -1;
+                const bool vec_f = (col_f + 32 <= prm.cols) && ((prm.cols & 3) == 0);
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    o[rr] = __shfl_sync(0xffffffffu, my_f, 4 * rr + (lane >> 3));
+                    m[rr] = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (vec_f && use_mask && o[rr] >= 0) m[rr] = __ldg(reinterpret_cast<const float4 *>(prm.mask + o[rr] + 4 * (lane & 7)));
+                }
+            };
+            fetch(0, off, mk);
             for (int cc = 0; cc < ncol_half; cc += 32) {
                 const int col0 = half * ncol_half + cc;
                 const int col = cb * N + col0;
                 const long long my_off = (row < prm.rows && col < prm.cols) ? row_off + col : -1;
                 const bool vec = (col + 32 <= prm.cols) && ((prm.cols & 3) == 0);
-                // offsets of the 8 lines this lane will store, and their mask values, fetched before the
-                // accumulator is even read so that the memory latency hides behind the TMEM load and the turn
-                long long off[8];
-                float4 mk[8];
-#pragma unroll
-                for (int rr = 0; rr < 8; ++rr) {
-                    off[rr] = __shfl_sync(0xffffffffu, my_off, 4 * rr + (lane >> 3));
-                    mk[rr] = make_float4(1.f, 1.f, 1.f, 1.f);
-                    if (vec && use_mask && off[rr] >= 0) mk[rr] = __ldg(reinterpret_cast<const float4 *>(prm.mask + off[rr] + 4 * (lane & 7)));
-                }
+                const bool more = cc + 32 < ncol_half;
+                if (more) fetch(cc + 32, off_nx, mk_nx);
                 if (cc == 0) {   // first chunk of the unit: only now wait for the accumulator
                     if (!mbar_wait_warp(accf_bar(buf), acc_use[buf] & 1u, abort_flag, 0x800u | (ew << 4) | buf)) { ok = false; break; }
                     acc_use[buf]++;
@@ -566,6 +575,10 @@ conv_grad_gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_
                         }
                         prm.out[my_off + x] = v;
                     }
+                }
+                if (more) {
+#pragma unroll
+                    for (int rr = 0; rr < 8; ++rr) { off[rr] = off_nx[rr]; mk[rr] = mk_nx[rr]; }
                 }
             }
             if (!ok) break;
