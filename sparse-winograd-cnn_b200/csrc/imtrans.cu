@@ -573,10 +573,11 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_image_kernel(const float
     float *dst = dX + ((long long)b * C + c0) * HW;
     if (pitch == HW) {
         for (int k = threadIdx.x; k < nch * HW; k += 256) dst[k] = O[k];
-    } else {
-        for (int k = threadIdx.x; k < nch * HW; k += 256) {
-            const int c = k / HW;
-            dst[k] = O[c * pitch + (k - c * HW)];
+    } else {   // a warp per channel: no division per element, and the channels' runs are adjacent in dX
+        for (int c = warp; c < nch; c += 8) {
+            const float *src = O + c * pitch;
+            float *d = dst + c * HW;
+            for (int i = lane; i < HW; i += 32) d[i] = src[i];
         }
     }
 }
