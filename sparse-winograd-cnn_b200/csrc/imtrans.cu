@@ -582,6 +582,85 @@ __global__ void __launch_bounds__(256) imtrans_bwd_nchw_image_kernel(const float
     }
 }
 
+// The same with two channels per lane (8-byte loads, a warp covers a tile x 64 channels): half the instructions per byte,
+// which is what this kernel is short of.  The image is kept as [pixel][channel] (channels innermost, so that the lanes'
+// 8-byte read-modify-writes are conflict-free) with a pitch of CB + 2 floats, and leaves per channel through strided
+// reads (two-way bank conflicts on the smaller side of the traffic).  Needs an even C and 8-byte aligned tensors.
+__device__ __forceinline__ float2 f2add(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 f2sub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ float2 f2neg(float2 a) { return make_float2(-a.x, -a.y); }
+
+template <bool MASK>
+__global__ void __launch_bounds__(256, 4) imtrans_bwd_nchw_image2_kernel(const float *__restrict__ dV, const float *__restrict__ Vm,
+                                                                           float *__restrict__ dX, int B, int H, int W, int C, int nH,
+                                                                           int nW, int CB)
+{
+    extern __shared__ __align__(16) float O[];     // [H*W][CB + 2]
+    const int b = blockIdx.x, c0 = blockIdx.y * CB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int HW = H * W, CBP = CB + 2;
+    const int nch = min(CB, C - c0);
+    const int ngr = (nch + 63) >> 6;               // groups of 64 channels
+    const long long plane = (long long)B * nH * nW * C;
+    for (int k = threadIdx.x; k < HW * CBP / 2; k += 256) reinterpret_cast<float2 *>(O)[k] = make_float2(0.f, 0.f);
+    __syncthreads();
+#pragma unroll 1
+    for (int pc = 0; pc < 4; ++pc) {
+        const int pr = pc >> 1, pq = pc & 1;
+        const int ntr = (nH - pr + 1) >> 1, ntc = (nW - pq + 1) >> 1;
+        const int items = ntr * ntc * ngr;
+#pragma unroll 1
+        for (int tt = warp; tt < items; tt += 8) {
+            const int gr = tt % ngr, t2 = tt / ngr;
+            const int th = 2 * (t2 / ntc) + pr, tw = 2 * (t2 % ntc) + pq;
+            const int cl = gr * 64 + 2 * lane;
+            if (cl < nch) {
+                const long long base = (((long long)b * nH + th) * nW + tw) * C + c0 + cl;
+                float2 g[4][4];
+#pragma unroll
+                for (int t = 0; t < 16; ++t) g[t >> 2][t & 3] = __ldg(reinterpret_cast<const float2 *>(dV + base + (long long)t * plane));
+                if (MASK) {
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        const float2 v = __ldg(reinterpret_cast<const float2 *>(Vm + base + (long long)t * plane));
+                        if (!(v.x > 0.f)) g[t >> 2][t & 3].x = 0.f;
+                        if (!(v.y > 0.f)) g[t >> 2][t & 3].y = 0.f;
+                    }
+                }
+                // d = B g B^T: along one axis (u0..u3) -> (u0, u1 - u2 + u3, -u0 + u1 + u2, -u3); rows in place
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 u1 = g[1][j], u2 = g[2][j];
+                    g[1][j] = f2add(f2sub(u1, u2), g[3][j]);
+                    g[2][j] = f2sub(f2add(u1, u2), g[0][j]);
+                    g[3][j] = f2neg(g[3][j]);
+                }
+                float *o = O + cl;
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const int h = 2 * th - 1 + y;
+                    if (h < 0 || h >= H) continue;
+                    const float2 d0 = g[y][0], d1 = f2add(f2sub(g[y][1], g[y][2]), g[y][3]), d2 = f2sub(f2add(g[y][1], g[y][2]), g[y][0]),
+                                 d3 = f2neg(g[y][3]);
+                    const int w0 = 2 * tw - 1;
+                    float *row = o + (h * W + w0) * CBP;
+                    if (w0 >= 0) { float2 *q = reinterpret_cast<float2 *>(row); *q = f2add(*q, d0); }
+                    { float2 *q = reinterpret_cast<float2 *>(row + CBP); *q = f2add(*q, d1); }
+                    if (w0 + 2 < W) { float2 *q = reinterpret_cast<float2 *>(row + 2 * CBP); *q = f2add(*q, d2); }
+                    if (w0 + 3 < W) { float2 *q = reinterpret_cast<float2 *>(row + 3 * CBP); *q = f2add(*q, d3); }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // a warp per channel: its H*W pixels are one contiguous run of dX, and the channels' runs are adjacent
+    float *dst = dX + ((long long)b * C + c0) * HW;
+    for (int c = warp; c < nch; c += 8) {
+        float *d = dst + c * HW;
+        for (int i = lane; i < HW; i += 32) d[i] = O[i * CBP + c];
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
@@ -678,6 +757,21 @@ int imtrans_bwd(const float *dV, const float *Vm, float *dX, int B, int H, int W
         const int HW = H * W;
         if (HW <= 200 && (long long)B * cdiv(C, HW <= 64 ? 128 : 64) >= 2LL * kNumSMs && B <= 0x7fffffff) {
             const int CB = HW <= 64 ? 128 : 64;
+            const auto aligned8 = [](const void *q) { return (reinterpret_cast<uintptr_t>(q) & 7u) == 0; };
+            if ((C & 1) == 0 && aligned8(dV) && (!Vm || aligned8(Vm)) && cdiv(C, CB) <= 65535) {      // two channels per lane
+                const int smem2 = HW * (CB + 2) * (int)sizeof(float);
+                const dim3 grid2((unsigned)B, cdiv(C, CB));
+                if (Vm) {
+                    if (cudaFuncSetAttribute(imtrans_bwd_nchw_image2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess)
+                        return WG2X2_ERR_LAUNCH;
+                    imtrans_bwd_nchw_image2_kernel<true><<<grid2, 256, smem2, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, CB);
+                } else {
+                    if (cudaFuncSetAttribute(imtrans_bwd_nchw_image2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess)
+                        return WG2X2_ERR_LAUNCH;
+                    imtrans_bwd_nchw_image2_kernel<false><<<grid2, 256, smem2, st>>>(dV, Vm, dX, B, H, W, C, nH, nW, CB);
+                }
+                return launch_status();
+            }
             const int pitch = HW | 1;
             const int smem = CB * pitch * (int)sizeof(float);
             if (cdiv(C, CB) <= 65535) {

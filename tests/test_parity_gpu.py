@@ -157,9 +157,10 @@ _VEC_FWD = [(150, 7, 7, 512), (160, 5, 8, 388), (30, 13, 14, 640), (150, 13, 14,
 
 
 @pytest.mark.parametrize("use_mask", [False, True])
-@pytest.mark.parametrize("shape", _VEC_BWD + [(3, 7, 7, 132), (2, 9, 11, 68), (1, 12, 100, 64), (2, 6, 6, 130)])
+@pytest.mark.parametrize("shape", _VEC_BWD + [(3, 7, 7, 132), (2, 9, 11, 68), (1, 12, 100, 64), (2, 6, 6, 130), (150, 7, 7, 255)])
 def test_imtrans_bwd_nchw_channel_vector_paths(wg, oracle, shape, use_mask):
-    """The NCHW gather's 16-byte-load variants (and small shapes that fall back from them), odd sizes included."""
+    """The NCHW gather's 16-byte-load variants (and small shapes that fall back from them), odd sizes included; the first
+    shapes with small images take the whole-image kernels (two channels per lane; one per lane for the odd channel count)."""
     B, H, W, C = shape
     rng = np.random.default_rng(23)
     nH, nW = (H + 1) // 2, (W + 1) // 2
