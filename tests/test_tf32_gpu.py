@@ -461,3 +461,24 @@ def test_pair_of_sms_kernel_equals_the_one_cta_kernel(tmp_path):
     for key in ("dV", "dW", "Y"):
         assert np.array_equal(outs[0][key], outs[1][key]), key
     assert np.isfinite(outs[0]["dW"]).all() and float(np.abs(outs[0]["dW"]).max()) > 0
+
+
+def test_pair_of_sms_kernel_repeated_launches(wg):
+    """300 back-to-back gradient and wide-forward products on the pair kernel (dW contracts over 1120 tiles, the
+    products over 512 channels): the cross-CTA barriers keep their phases from launch to launch, every result
+    equals the first bit for bit and no bounded wait gives up."""
+    g = torch.Generator().manual_seed(5)
+    B, C, K, H, W = 70, 512, 512, 7, 7
+    X = torch.randn((B, C, H, W), generator=g).cuda()
+    Wt = (0.05 * torch.randn((16, C, K), generator=g)).cuda()
+    dY = torch.randn((B, K, H, W), generator=g).cuda()
+    V = wg.imtrans_fwd(X, relu=True, layout="NCHW")
+    prep = wg.prepare_weights(Wt)
+    dV0, dW0 = wg.conv_bwd(V, Wt, dY, layout="NCHW", relu=False, math="tf32")
+    Y0 = wg.conv_fwd_prepared(V, prep, K, H, W, layout="NCHW")
+    for i in range(300):
+        dV, dW = wg.conv_bwd(V, Wt, dY, layout="NCHW", relu=False, math="tf32")
+        Y = wg.conv_fwd_prepared(V, prep, K, H, W, layout="NCHW")
+        if i % 60 == 59:
+            _status_ok(wg)
+            assert torch.equal(dV, dV0) and torch.equal(dW, dW0) and torch.equal(Y, Y0), i
