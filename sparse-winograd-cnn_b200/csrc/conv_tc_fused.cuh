@@ -752,7 +752,7 @@ layer_fwd_fused_kernel(const __grid_constant__ CUtensorMap mapXd, const __grid_c
                         // (an empty group when nothing was issued: the count of groups per round stays the same)
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                    // the warp goes on together (tcgen05.ld is next) and with one verdict
+                    // the warp goes on together (tcgen05.ld is next) and with one outcome
                     if (!__all_sync(0xffffffffu, stored)) { ok = false; break; }
                     ++st_use;
                     if (++ybox == kFuYBoxes) ybox = 0;
