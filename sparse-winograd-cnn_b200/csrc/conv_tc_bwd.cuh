@@ -967,7 +967,10 @@ int conv_fwd_tc_wide(const float *V, const void *prepared, float *Y, int B, int 
         int R = 384 / (2 * outW);
         if (R < 1) R = 1;
         if (R > nH) R = nH;
+        // a small batch: lower bands, so that the grid still gives every SM a few blocks
+        while (R > 1 && (long long)B * cdiv(nH, R) * cdiv(K, 32) < 3LL * kNumSMs) --R;
         const int nbands = cdiv(nH, R);
+        R = cdiv(nH, nbands);
         const int pitch = (2 * R * outW) | 1;
         const int smem = 32 * pitch * (int)sizeof(float);
         if ((long long)B * nbands > 0x7fffffffLL || smem > 200 * 1024) return WG2X2_ERR_UNSUPPORTED;

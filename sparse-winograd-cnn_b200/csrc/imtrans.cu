@@ -714,7 +714,10 @@ int imtrans_fwd(const float *X, float *V, int B, int H, int W, int C, int layout
             int R = (kBandFloats / W - 2) / 2;
             if (R < 1) R = 1;
             if (R > nH) R = nH;
+            // a small batch: lower bands, so that the grid still gives every SM a few blocks
+            while (R > 1 && (long long)B * cdiv(nH, R) * cdiv(C, 32) < 3LL * kNumSMs) --R;
             const int nbands = cdiv(nH, R);
+            R = cdiv(nH, nbands);
             const int pitch = ((2 * R + 2) * W) | 1;
             const int smem = 32 * pitch * (int)sizeof(float);
             const long long gxb = (long long)B * nbands;
