@@ -58,6 +58,41 @@ __global__ void __launch_bounds__(256) maxpool_vec_kernel(const float *__restric
     }
 }
 
+// Two consecutive outputs of a row per thread, for widths that are multiples of 4 but not of 8 (28 -> 14): input columns
+// 4t .. 4t+4 of three rows = one 16-byte load and one scalar per row; the output pair is one 8-byte store.
+template <bool RELU_OUT>
+__global__ void __launch_bounds__(256) maxpool_vec2_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
+                                                             const float *__restrict__ rs, const float *__restrict__ rb, int C,
+                                                             long long planes, int H, int W, int OH, int OW, int ph)
+{
+    const int OW2 = OW >> 1;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= planes * OH * OW2) return;
+    const int t = (int)(idx % OW2);
+    const int oh = (int)((idx / OW2) % OH);
+    const long long pl = idx / ((long long)OW2 * OH);
+    const float *xp = X + pl * H * W;
+    const float ninf = -__int_as_float(0x7f800000);
+    float m[5] = {ninf, ninf, ninf, ninf, ninf};
+#pragma unroll
+    for (int dy = 0; dy < 3; ++dy) {
+        const int h = 2 * oh - ph + dy;
+        if (h < 0 || h >= H) continue;
+        const float *row = xp + (long long)h * W + 4 * t;
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(row));
+        const float c = (4 * t + 4 < W) ? __ldg(row + 4) : ninf;
+        m[0] = fmaxf(m[0], a.x); m[1] = fmaxf(m[1], a.y); m[2] = fmaxf(m[2], a.z); m[3] = fmaxf(m[3], a.w);
+        m[4] = fmaxf(m[4], c);
+    }
+    const float2 o = make_float2(fmaxf(fmaxf(m[0], m[1]), m[2]), fmaxf(fmaxf(m[2], m[3]), m[4]));
+    const long long off = (pl * OH + oh) * OW + 2 * t;
+    *reinterpret_cast<float2 *>(Y + off) = o;
+    if (RELU_OUT) {
+        const float sc = rs ? __ldg(rs + (int)(pl % C)) : 1.f, sh = rs ? __ldg(rb + (int)(pl % C)) : 0.f;
+        *reinterpret_cast<float2 *>(Yr + off) = make_float2(fmaxf(fmaf(o.x, sc, sh), 0.f), fmaxf(fmaf(o.y, sc, sh), 0.f));
+    }
+}
+
 // Any size: one output per thread.
 template <bool RELU_OUT>
 __global__ void __launch_bounds__(256) maxpool_any_kernel(const float *__restrict__ X, float *__restrict__ Y, float *__restrict__ Yr,
@@ -165,6 +200,12 @@ int maxpool3x3s2_same(const float *X, float *Y, float *Yrelu, const float *rs, c
         if (blocks > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
         if (Yrelu) maxpool_vec_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
         else       maxpool_vec_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
+    } else if ((W % 4) == 0 && al16(X) && al16(Y) && (!Yrelu || al16(Yrelu))) {
+        const long long total = planes * OH * (OW / 2);
+        const long long blocks = cdivll(total, 256);
+        if (blocks > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;
+        if (Yrelu) maxpool_vec2_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
+        else       maxpool_vec2_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(X, Y, Yrelu, rs, rb, C, planes, H, W, OH, OW, ph);
     } else {
         const long long blocks = cdivll(planes * OH * OW, 256);
         if (blocks > 0x7fffffffLL) return WG2X2_ERR_UNSUPPORTED;

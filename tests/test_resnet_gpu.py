@@ -60,7 +60,7 @@ def test_same_pool_matches_tensorflow_padding():
         assert torch.equal(_same_pool(x), ref)
 
 
-@pytest.mark.parametrize("shape", [(3, 8, 112, 112), (2, 64, 32, 40), (1, 96, 9, 11), (2, 5, 56, 56), (2, 4, 28, 28), (2, 3, 14, 14), (2, 3, 7, 7), (1, 2, 14, 9),
+@pytest.mark.parametrize("shape", [(3, 8, 112, 112), (2, 64, 32, 40), (1, 96, 9, 11), (2, 5, 56, 56), (2, 4, 28, 28), (1, 3, 9, 12), (2, 2, 13, 20), (2, 3, 14, 14), (2, 3, 7, 7), (1, 2, 14, 9),
                                    (1, 2, 5, 8), (2, 3, 9, 16), (1, 1, 1, 1), (1, 2, 2, 3)])
 def test_pool_kernel_matches_torch(shape):
     """wg2x2_maxpool3x3s2_same (the vector path for widths that are multiples of 8, the general path elsewhere, odd
